@@ -28,7 +28,8 @@ class RopeScaling:
     """Frequency rescaling rule of a rotary position encoding.
 
     ``rope_type == "llama3"`` is the piecewise rule of
-    src/op/kernels/cpu/rope_kernel.cpp:117-139.
+    src/op/kernels/cpu/rope_kernel.cpp:117-139.  ``rope_type == "yarn"`` is a ramp over the frequencies (position
+    kind "rope_yarn"), whose two turn counts ``fast`` and ``slow`` travel as high_freq_factor and low_freq_factor.
     """
     rope_type: str
     factor: float
@@ -160,6 +161,9 @@ class LayerRun:
     ``stream_input``: row of the model's table of stream inputs (``ModelConfig.stream_inputs`` rows of
     hidden_size, a weight of the model) that is added to every token's residual stream right before
     this run; None = nothing.  A model that runs a span of layers several times marks each pass so.
+    With ``ModelConfig.stream_input_kind`` "project_with_embedding" the mark means instead: right before this
+    run the stream x becomes W [x; x0], x0 being what the embedding produced and W one [hidden, 2 hidden] weight
+    of the model (the number is the pass and selects nothing).
     """
     layer: int
     cache_of: Optional[int] = None
@@ -182,6 +186,7 @@ class ModelConfig:
     embedding: EmbeddingSpec = field(default_factory=EmbeddingSpec)
     head: HeadSpec = field(default_factory=HeadSpec)
     stream_inputs: int = 0      # rows of the table that ``LayerRun.stream_input`` names (0: the model has none)
+    stream_input_kind: str = "row"      # "row": a table row is added; "project_with_embedding": x <- W [x; x0]
 
     @property
     def num_layers(self) -> int:
@@ -205,6 +210,8 @@ class ModelConfig:
             raise ConfigError("a model needs at least one layer")
         if not self.schedule:
             raise ConfigError("the schedule is empty")
+        if self.stream_input_kind not in ("row", "project_with_embedding"):
+            raise ConfigError(f"stream_input_kind '{self.stream_input_kind}' is not known (row, project_with_embedding)")
         for r, run in enumerate(self.schedule):
             if not 0 <= run.layer < len(self.layers):
                 raise ConfigError(f"schedule[{r}] names layer {run.layer}, "

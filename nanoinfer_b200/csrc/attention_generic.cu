@@ -7,6 +7,8 @@
 // score: a position encoding that acts on the scores instead of rotating queries and keys.
 // An optional cap bounds the scaled score smoothly: s <- cap * tanh(s / cap) (cap = 0: none), FP32, before
 // the bias and the softmax.
+// Values may have a size of their own (v_dim): the value pages are then [P, Hkv, page, v_dim] and the output
+// [T, Hq, v_dim].
 //
 // The result of a token depends only on its own keys and their order, never on how the
 // step was cut or what else is in the batch, so this kernel is the FP32 path's attention
@@ -29,7 +31,7 @@ __global__ void attention_generic_kernel(const T* __restrict__ q, const T* __res
                                          const int* __restrict__ block_table, int bt_stride,
                                          int n_tokens, int n_q_heads, int n_kv_heads, int head_dim,
                                          int page_size, int window, float scale,
-                                         const float* __restrict__ head_slopes, float score_cap) {
+                                         const float* __restrict__ head_slopes, float score_cap, int v_dim) {
     const int warps_per_block = blockDim.x >> 5;
     const long long item = (long long)blockIdx.x * warps_per_block + (threadIdx.x >> 5);
     if (item >= (long long)n_tokens * n_q_heads) return;
@@ -54,9 +56,9 @@ __global__ void attention_generic_kernel(const T* __restrict__ q, const T* __res
     float m = -INFINITY, l = 0.f;
     for (int j = lo; j <= pos; ++j) {
         const int page = table[j / page_size];
-        const size_t off = (((size_t)page * n_kv_heads + kvh) * page_size + (j % page_size)) * head_dim;
-        const T* krow = k_pages + off;
-        const T* vrow = v_pages + off;
+        const size_t slot = ((size_t)page * n_kv_heads + kvh) * page_size + (j % page_size);
+        const T* krow = k_pages + slot * head_dim;
+        const T* vrow = v_pages + slot * v_dim;
         float dot = 0.f;
 #pragma unroll
         for (int r = 0; r < ATT_MAX_REGS; ++r) {
@@ -74,16 +76,16 @@ __global__ void attention_generic_kernel(const T* __restrict__ q, const T* __res
 #pragma unroll
         for (int r = 0; r < ATT_MAX_REGS; ++r) {
             const int dim = lane + 32 * r;
-            if (dim < head_dim) acc[r] = acc[r] * corr + p * ni_to_float(vrow[dim]);
+            if (dim < v_dim) acc[r] = acc[r] * corr + p * ni_to_float(vrow[dim]);
         }
         m = m_new;
     }
-    T* orow = out + ((size_t)t * n_q_heads + head) * head_dim;
+    T* orow = out + ((size_t)t * n_q_heads + head) * v_dim;
     const float inv = 1.0f / l;
 #pragma unroll
     for (int r = 0; r < ATT_MAX_REGS; ++r) {
         const int dim = lane + 32 * r;
-        if (dim < head_dim) orow[dim] = ni_from_float<T>(acc[r] * inv);
+        if (dim < v_dim) orow[dim] = ni_from_float<T>(acc[r] * inv);
     }
 }
 
@@ -92,11 +94,12 @@ NI_EXPORT int ni_attention_generic(const void* q, int dtype, const void* k_pages
                                    const int* positions, const int* seq_of_token, const int* block_table, int bt_stride,
                                    int n_tokens, int n_q_heads, int n_kv_heads, int head_dim,
                                    int page_size, int window, float scale, const float* head_slopes,
-                                   float score_cap, cudaStream_t stream) {
+                                   float score_cap, int v_dim, cudaStream_t stream) {
     if (n_tokens <= 0) return NI_OK;
-    if (n_q_heads <= 0 || n_kv_heads <= 0 || n_q_heads % n_kv_heads || head_dim <= 0 || page_size <= 0)
+    if (n_q_heads <= 0 || n_kv_heads <= 0 || n_q_heads % n_kv_heads || head_dim <= 0 || page_size <= 0 || v_dim < 0)
         return NI_ERR_BAD_ARGUMENT;
-    if (head_dim > 32 * 16) return NI_ERR_UNSUPPORTED_SIZE;
+    if (v_dim == 0) v_dim = head_dim;          // values of the keys' size
+    if (head_dim > 32 * 16 || v_dim > 32 * 16) return NI_ERR_UNSUPPORTED_SIZE;
     const int warps = 4;
     const long long items = (long long)n_tokens * n_q_heads;
     const long long blocks = (items + warps - 1) / warps;
@@ -105,10 +108,10 @@ NI_EXPORT int ni_attention_generic(const void* q, int dtype, const void* k_pages
     attention_generic_kernel<T, R><<<(int)blocks, warps * 32, 0, stream>>>(                         \
         (const T*)q, (const T*)k_pages, (const T*)v_pages, (T*)out, token_list, positions,         \
         seq_of_token,                                                                               \
-        block_table, bt_stride, n_tokens, n_q_heads, n_kv_heads, head_dim, page_size, window, scale, head_slopes, score_cap)
+        block_table, bt_stride, n_tokens, n_q_heads, n_kv_heads, head_dim, page_size, window, scale, head_slopes, score_cap, v_dim)
 #define LAUNCH(T)                          \
     do {                                   \
-        if (head_dim <= 256) LAUNCH_R(T, 8); \
+        if (head_dim <= 256 && v_dim <= 256) LAUNCH_R(T, 8); \
         else LAUNCH_R(T, 16);              \
     } while (0)
     if (dtype == NI_DTYPE_F32) LAUNCH(float);

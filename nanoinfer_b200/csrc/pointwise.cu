@@ -293,21 +293,22 @@ NI_EXPORT int ni_scale_f32(float* x, float factor, long long n, cudaStream_t str
 // out = g * sigmoid(slope * g) * (u + shift); gate_up = [gate | up] along the columns.
 template <typename T>
 __global__ void capped_glu_kernel(const T* __restrict__ gate_up, T* __restrict__ out, long long n, int inter,
-                                  float limit, float slope, float shift) {
+                                  float limit, float slope, float shift, const float* __restrict__ row_scale) {
     const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= n) return;
     const long long t = i / inter;
     const int c = (int)(i - t * inter);
     const T* row = gate_up + (size_t)t * 2 * inter;
-    const float g = fminf(ni_to_float(row[c]), limit);
-    const float u = fminf(fmaxf(ni_to_float(row[inter + c]), -limit), limit);
+    const float rs = row_scale ? row_scale[t] : 1.0f;
+    const float g = fminf(ni_to_float(row[c]) * rs, limit);
+    const float u = fminf(fmaxf(ni_to_float(row[inter + c]) * rs, -limit), limit);
     out[i] = ni_from_float<T>(g / (1.0f + expf(-slope * g)) * (u + shift));
 }
 
 // The same, 16 bytes per thread (row widths that are multiples of 8 bfloat16 or 4 float values).
 template <typename T>
 __global__ void capped_glu_vec_kernel(const T* __restrict__ gate_up, T* __restrict__ out, long long n_vec, int inter,
-                                      float limit, float slope, float shift) {
+                                      float limit, float slope, float shift, const float* __restrict__ row_scale) {
     constexpr int V = NiVec16<T>::N;
     const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= n_vec) return;
@@ -318,16 +319,19 @@ __global__ void capped_glu_vec_kernel(const T* __restrict__ gate_up, T* __restri
     float g[V], u[V], o[V];
     NiVec16<T>::load(row + c, g);
     NiVec16<T>::load(row + inter + c, u);
+    const float rs = row_scale ? row_scale[t] : 1.0f;
 #pragma unroll
     for (int k = 0; k < V; ++k) {
-        const float gg = fminf(g[k], limit), uu = fminf(fmaxf(u[k], -limit), limit);
+        const float gg = fminf(g[k] * rs, limit), uu = fminf(fmaxf(u[k] * rs, -limit), limit);
         o[k] = gg / (1.0f + expf(-slope * gg)) * (uu + shift);
     }
     NiVec16<T>::store(out + (size_t)t * inter + c, o);
 }
 
+// row_scale (FP32 [rows], or null): the row's gate and up values are multiplied by it before the limits, which is
+// what a unit computes when its INPUT was multiplied by that number (both products are linear in the input).
 NI_EXPORT int ni_capped_glu(const void* gate_up, void* out, int dtype, int n_rows, int inter, float limit, float slope,
-                            float shift, cudaStream_t stream) {
+                            float shift, const float* row_scale, cudaStream_t stream) {
     if (n_rows <= 0) return NI_OK;
     if (inter <= 0) return NI_ERR_BAD_ARGUMENT;
     const long long n = (long long)n_rows * inter, blocks = (n + 255) / 256;
@@ -335,20 +339,20 @@ NI_EXPORT int ni_capped_glu(const void* gate_up, void* out, int dtype, int n_row
     if (dtype == NI_DTYPE_BF16 && inter % 8 == 0) {
         const long long nv = n / 8;
         capped_glu_vec_kernel<__nv_bfloat16><<<(int)((nv + 255) / 256), 256, 0, stream>>>(
-            (const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, nv, inter, limit, slope, shift);
+            (const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, nv, inter, limit, slope, shift, row_scale);
         NI_RETURN_LAUNCH_STATUS();
     }
     if (dtype == NI_DTYPE_F32 && inter % 4 == 0) {
         const long long nv = n / 4;
         capped_glu_vec_kernel<float><<<(int)((nv + 255) / 256), 256, 0, stream>>>((const float*)gate_up, (float*)out, nv, inter,
-                                                                                limit, slope, shift);
+                                                                                limit, slope, shift, row_scale);
         NI_RETURN_LAUNCH_STATUS();
     }
     if (dtype == NI_DTYPE_F32)
-        capped_glu_kernel<float><<<(int)blocks, 256, 0, stream>>>((const float*)gate_up, (float*)out, n, inter, limit, slope, shift);
+        capped_glu_kernel<float><<<(int)blocks, 256, 0, stream>>>((const float*)gate_up, (float*)out, n, inter, limit, slope, shift, row_scale);
     else if (dtype == NI_DTYPE_BF16)
         capped_glu_kernel<__nv_bfloat16><<<(int)blocks, 256, 0, stream>>>((const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, n,
-                                                                         inter, limit, slope, shift);
+                                                                         inter, limit, slope, shift, row_scale);
     else return NI_ERR_BAD_ARGUMENT;
     NI_RETURN_LAUNCH_STATUS();
 }
@@ -377,5 +381,75 @@ NI_EXPORT int ni_embedding_scaled(const int* tokens, const void* table, int tabl
                                                                                 out, d, vocab);
     else
         return NI_ERR_BAD_ARGUMENT;
+    NI_RETURN_LAUNCH_STATUS();
+}
+
+// out[t, :] = [a[t, :] | b[t, :]] in the activations' type: two FP32 streams side by side as one product's input.
+template <typename T>
+__global__ void concat_cast_kernel(const float* __restrict__ a, const float* __restrict__ b, T* __restrict__ out, int d) {
+    const int t = blockIdx.x;
+    const float* ar = a + (size_t)t * d;
+    const float* br = b + (size_t)t * d;
+    T* o = out + (size_t)t * 2 * d;
+    for (int i = threadIdx.x; i < d; i += blockDim.x) {
+        o[i] = ni_from_float<T>(ar[i]);
+        o[d + i] = ni_from_float<T>(br[i]);
+    }
+}
+
+NI_EXPORT int ni_concat_cast(const float* a, const float* b, void* out, int dtype, int n_rows, int d, cudaStream_t stream) {
+    if (n_rows <= 0) return NI_OK;
+    if (d <= 0) return NI_ERR_BAD_ARGUMENT;
+    const int threads = d >= 1024 ? 256 : 128;
+    if (dtype == NI_DTYPE_F32) concat_cast_kernel<float><<<n_rows, threads, 0, stream>>>(a, b, (float*)out, d);
+    else if (dtype == NI_DTYPE_BF16) concat_cast_kernel<__nv_bfloat16><<<n_rows, threads, 0, stream>>>(a, b, (__nv_bfloat16*)out, d);
+    else return NI_ERR_BAD_ARGUMENT;
+    NI_RETURN_LAUNCH_STATUS();
+}
+
+// out = max(z, 0)^2, element by element, FP32 inside.
+template <typename T>
+__global__ void relu_squared_kernel(const T* __restrict__ z, T* __restrict__ out, long long n) {
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const float v = fmaxf(ni_to_float(z[i]), 0.f);
+    out[i] = ni_from_float<T>(v * v);
+}
+
+// The same, 16 bytes per thread (counts that are multiples of 8 bfloat16 or 4 float values).
+template <typename T>
+__global__ void relu_squared_vec_kernel(const T* __restrict__ z, T* __restrict__ out, long long n_vec) {
+    constexpr int V = NiVec16<T>::N;
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n_vec) return;
+    float v[V];
+    NiVec16<T>::load(z + i * V, v);
+#pragma unroll
+    for (int k = 0; k < V; ++k) {
+        const float r = fmaxf(v[k], 0.f);
+        v[k] = r * r;
+    }
+    NiVec16<T>::store(out + i * V, v);
+}
+
+NI_EXPORT int ni_relu_squared(const void* z, void* out, int dtype, long long n, cudaStream_t stream) {
+    if (n <= 0) return NI_OK;
+    const int per = dtype == NI_DTYPE_BF16 ? 8 : 4;
+    if (dtype != NI_DTYPE_BF16 && dtype != NI_DTYPE_F32) return NI_ERR_BAD_ARGUMENT;
+    if (n % per == 0) {
+        const long long nv = n / per, blocks = (nv + 255) / 256;
+        if (blocks > 2147483647LL) return NI_ERR_UNSUPPORTED_SIZE;
+        if (dtype == NI_DTYPE_BF16)
+            relu_squared_vec_kernel<__nv_bfloat16><<<(int)blocks, 256, 0, stream>>>((const __nv_bfloat16*)z, (__nv_bfloat16*)out, nv);
+        else
+            relu_squared_vec_kernel<float><<<(int)blocks, 256, 0, stream>>>((const float*)z, (float*)out, nv);
+        NI_RETURN_LAUNCH_STATUS();
+    }
+    const long long blocks = (n + 255) / 256;
+    if (blocks > 2147483647LL) return NI_ERR_UNSUPPORTED_SIZE;
+    if (dtype == NI_DTYPE_BF16)
+        relu_squared_kernel<__nv_bfloat16><<<(int)blocks, 256, 0, stream>>>((const __nv_bfloat16*)z, (__nv_bfloat16*)out, n);
+    else
+        relu_squared_kernel<float><<<(int)blocks, 256, 0, stream>>>((const float*)z, (float*)out, n);
     NI_RETURN_LAUNCH_STATUS();
 }

@@ -1,0 +1,110 @@
+// What lies between the fused q | k | v projection and the attention of a mixer whose queries and keys are
+// normed as a whole: per token, in FP32 whatever the tensors' type,
+//
+//   q, k, v  += bias                         (optional; one FP32 vector over the projection's columns)
+//   q <- q / sqrt(mean(q^2) + eps) * gain    over ALL H * D query values at once, and likewise the G * D key
+//                                            values (optional; gains FP32 [H D] and [G D])
+//   rotation of the first `rotary_dim` dimensions of every head of q and k, dimension i paired with
+//            i + rotary_dim / 2:  (u, v) -> (u c - v s, v c + u s),  c = m cos(a), s = m sin(a),
+//            a = float(position) * inv_freq[i]  (m = `magnitude`: an encoding that also scales what it rotates)
+//   q -> q_out [T, H D];  k -> key pages [P, G, page, D];  v -> value pages [P, G, page, V]
+//
+// One block per token.  The row's queries and keys are widened once into shared memory, where the two sums of
+// squares and the partner of every rotated dimension are found; the angles' cosines and sines are computed
+// once per token and shared by all heads.
+#include "common.cuh"
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+qk_norm_rope_kernel(const T* __restrict__ qkv, int ld, const float* __restrict__ bias,
+                    const float* __restrict__ q_gain, const float* __restrict__ k_gain, float eps,
+                    const int* __restrict__ positions, const int* __restrict__ seq_of_token,
+                    const int* __restrict__ block_table, int bt_stride, const float* __restrict__ inv_freq,
+                    float magnitude, T* __restrict__ q_out, T* __restrict__ k_pages, T* __restrict__ v_pages,
+                    int H, int G, int D, int V, int rotary_dim, int page_size) {
+    extern __shared__ __align__(16) float sm[];
+    __shared__ float scratch[32];
+    const int nq = H * D, nk = G * D, nv = G * V, half = rotary_dim >> 1;
+    float* row = sm;                 // [nq + nk]: queries, then keys, bias added
+    float* cs = sm + nq + nk;        // [2 half]: m cos, then m sin
+    const int t = blockIdx.x;
+    const T* x = qkv + (size_t)t * ld;
+    const int pos = positions[t];
+    float sq = 0.f, sk = 0.f;
+    for (int i = threadIdx.x; i < nq + nk; i += blockDim.x) {
+        const float v = ni_to_float(x[i]) + (bias ? bias[i] : 0.f);
+        row[i] = v;
+        if (i < nq) sq += v * v; else sk += v * v;
+    }
+    for (int i = threadIdx.x; i < half; i += blockDim.x) {
+        float s, c;
+        sincosf((float)pos * inv_freq[i], &s, &c);
+        cs[i] = c * magnitude;
+        cs[half + i] = s * magnitude;
+    }
+    sq = ni_block_sum(sq, scratch);
+    sk = ni_block_sum(sk, scratch);          // (its barriers also publish row and cs)
+    const float inv_q = q_gain ? 1.0f / sqrtf(sq / (float)nq + eps) : 1.0f;
+    const float inv_k = k_gain ? 1.0f / sqrtf(sk / (float)nk + eps) : 1.0f;
+    T* kdst = nullptr;
+    T* vdst = nullptr;
+    if (k_pages) {
+        const int page = block_table[(size_t)seq_of_token[t] * bt_stride + pos / page_size];
+        const int in_page = pos % page_size;
+        kdst = k_pages + ((size_t)page * G * page_size + in_page) * D;           // head g: + g * page_size * D
+        vdst = v_pages + ((size_t)page * G * page_size + in_page) * V;
+    }
+    for (int i = threadIdx.x; i < nq + nk; i += blockDim.x) {
+        const bool is_q = i < nq;
+        const int e = is_q ? i : i - nq;
+        const int head = e / D, dim = e - head * D;
+        const float* gain = is_q ? q_gain : k_gain;
+        const float inv = is_q ? inv_q : inv_k;
+        float a = row[i] * inv * (gain ? gain[e] : 1.0f);
+        if (dim < rotary_dim) {
+            const bool first = dim < half;
+            const int other = first ? i + half : i - half, oe = first ? e + half : e - half;
+            const float b = row[other] * inv * (gain ? gain[oe] : 1.0f);
+            const int f = first ? dim : dim - half;
+            a = first ? a * cs[f] - b * cs[half + f] : a * cs[f] + b * cs[half + f];
+        }
+        if (is_q) q_out[(size_t)t * nq + e] = ni_from_float<T>(a);
+        else if (kdst) kdst[(size_t)head * page_size * D + dim] = ni_from_float<T>(a);
+    }
+    if (vdst) {
+        for (int i = threadIdx.x; i < nv; i += blockDim.x) {
+            const int head = i / V, dim = i - head * V;
+            const float v = ni_to_float(x[nq + nk + i]) + (bias ? bias[nq + nk + i] : 0.f);
+            vdst[(size_t)head * page_size * V + dim] = ni_from_float<T>(v);
+        }
+    }
+}
+
+// qkv [T, ld] with columns q (H D) | k (G D) | v (G V); bias FP32 [H D + G D + G V] or null; q_gain FP32 [H D] and
+// k_gain FP32 [G D], or null for no norm; k_pages / v_pages null: nothing is written (a run that reads another's cache).
+NI_EXPORT int ni_qk_norm_rope(const void* qkv, int dtype, int ld, const float* bias, const float* q_gain,
+                              const float* k_gain, float eps, const int* positions, const int* seq_of_token,
+                              const int* block_table, int bt_stride, const float* inv_freq, float magnitude, void* q_out,
+                              void* k_pages, void* v_pages, int n_tokens, int H, int G, int D, int V, int rotary_dim,
+                              int page_size, cudaStream_t stream) {
+    if (n_tokens <= 0) return NI_OK;
+    if (H <= 0 || G <= 0 || D <= 0 || V <= 0 || page_size <= 0 || rotary_dim < 0 || rotary_dim > D || (rotary_dim & 1) ||
+        ld < (H + G) * D + G * V || (q_gain == nullptr) != (k_gain == nullptr))
+        return NI_ERR_BAD_ARGUMENT;
+    const size_t smem = ((size_t)(H + G) * D + rotary_dim) * sizeof(float);
+    if (smem > 200 * 1024) return NI_ERR_UNSUPPORTED_SIZE;
+#define LAUNCH(T)                                                                                                    \
+    do {                                                                                                             \
+        if (smem > 48 * 1024)                                                                                        \
+            cudaFuncSetAttribute(qk_norm_rope_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);   \
+        qk_norm_rope_kernel<T><<<n_tokens, 256, smem, stream>>>((const T*)qkv, ld, bias, q_gain, k_gain, eps,       \
+                                                                positions, seq_of_token, block_table, bt_stride,     \
+                                                                inv_freq, magnitude, (T*)q_out, (T*)k_pages,         \
+                                                                (T*)v_pages, H, G, D, V, rotary_dim, page_size);     \
+    } while (0)
+    if (dtype == NI_DTYPE_F32) LAUNCH(float);
+    else if (dtype == NI_DTYPE_BF16) LAUNCH(__nv_bfloat16);
+    else return NI_ERR_BAD_ARGUMENT;
+#undef LAUNCH
+    NI_RETURN_LAUNCH_STATUS();
+}

@@ -1,8 +1,13 @@
 // A routed feed-forward: every token chooses a few of many small gated units ("experts").
 //
-//   route     z = W_router x, s = softmax(z) over all experts, all FP32; the `top` experts with the largest
-//             s + bias are chosen (ties: the lower index), their weights are s (optionally divided by their sum).
-//             Experts numbered n_real and above are identity experts: their output is x itself.
+//   route     z = W_router x, s = softmax(z) over all experts - or s = sigmoid(z), each expert on its own -, all FP32;
+//             the `top` experts with the largest s + bias are chosen (ties: the lower index), their weights are s
+//             (optionally divided by their sum).  Experts numbered n_real and above are identity experts: their
+//             output is x itself.
+//   unit      an expert is W_down act(W_gate x, W_up x) with act(g, u) = g' * sigmoid(slope * g') * (u' + shift),
+//             g' = min(r g, limit), u' = clamp(r u, -limit, limit): limit = infinity, slope = 1, shift = 0, r = 1 is
+//             silu(g) * u; r is a number per row - the token's weight where a design multiplies the expert's INPUT by
+//             it (both products are linear in the input, so the factor is applied to their results, in FP32)
 //   layout    the (token, choice) pairs are laid out expert by expert (layout + scatter; where a pair lands
 //             inside its expert's stretch is decided by an atomic counter and changes no result, since every
 //             row is computed on its own)
@@ -28,7 +33,7 @@ __global__ void __launch_bounds__(RT_ROUTE_WARPS * 32)
 route_kernel(const T* __restrict__ x, const float* __restrict__ w_router,
              const float* __restrict__ bias, int* __restrict__ ids, float* __restrict__ weights,
              int* __restrict__ counts, int n_tokens, int d, int n_all, int n_real, int top,
-             int renormalize) {
+             int renormalize, int sigmoid_scores, float* __restrict__ all_scores) {
     extern __shared__ __align__(16) float xs[];          // [d]
     __shared__ float choice[RT_MAX_EXPERTS];
     __shared__ float score[RT_MAX_EXPERTS];
@@ -58,21 +63,25 @@ route_kernel(const T* __restrict__ x, const float* __restrict__ w_router,
     }
     __syncthreads();
     if (w != 0) return;
-    float m = -INFINITY;
-    for (int e = lane; e < n_all; e += 32) m = fmaxf(m, score[e]);
-    m = ni_warp_max(m);
-    float sum = 0.f;
-    for (int e = lane; e < n_all; e += 32) {
-        const float p = expf(score[e] - m);
-        score[e] = p;
-        sum += p;
+    float inv = 1.0f;
+    if (!sigmoid_scores) {
+        float m = -INFINITY;
+        for (int e = lane; e < n_all; e += 32) m = fmaxf(m, score[e]);
+        m = ni_warp_max(m);
+        float sum = 0.f;
+        for (int e = lane; e < n_all; e += 32) {
+            const float p = expf(score[e] - m);
+            score[e] = p;
+            sum += p;
+        }
+        sum = ni_warp_sum(sum);
+        inv = 1.0f / sum;
     }
-    sum = ni_warp_sum(sum);
-    const float inv = 1.0f / sum;
     for (int e = lane; e < n_all; e += 32) {
-        const float s = score[e] * inv;
+        const float s = sigmoid_scores ? 1.0f / (1.0f + expf(-score[e])) : score[e] * inv;
         score[e] = s;
         choice[e] = s + (bias ? bias[e] : 0.f);
+        if (all_scores && e < n_real) all_scores[(size_t)t * n_real + e] = s;      // every real expert's score, chosen or not
     }
     __syncwarp();
     float wsum = 0.f;
@@ -125,7 +134,7 @@ __global__ void layout_kernel(int* __restrict__ counts, int* __restrict__ offset
 
 __global__ void scatter_kernel(const int* __restrict__ ids, const int* __restrict__ offsets, int* __restrict__ cursor,
                                int* __restrict__ row_of_pair, int* __restrict__ token_of_row, int n_pairs, int top,
-                               int n_real) {
+                               int n_real, const float* __restrict__ weights, float* __restrict__ weight_of_row) {
     const int p = blockIdx.x * blockDim.x + threadIdx.x;
     if (p >= n_pairs) return;
     const int e = ids[p];
@@ -136,11 +145,22 @@ __global__ void scatter_kernel(const int* __restrict__ ids, const int* __restric
     const int row = offsets[e] + atomicAdd(&cursor[e], 1);
     row_of_pair[p] = row;
     token_of_row[row] = p / top;
+    if (weight_of_row) weight_of_row[row] = weights[p];
 }
 
 // out[row, :] = a[row or its token, :] . w[expert of the row]^T for every row of every expert's stretch.
 // 64 x 64 tiles, 16 x 16 threads with 4 x 4 outputs each; ACT: the matrix holds gate rows [0, N) and up rows
 // [N, 2N) and the result is silu(gate) * up.
+// limit, slope, shift of a unit's activation, and the row's factor (see the head of this file)
+struct RtAct {
+    float limit, slope, shift;
+};
+__device__ __forceinline__ float rt_act(float g, float u, const RtAct a, float r) {
+    g = fminf(g * r, a.limit);
+    u = fminf(fmaxf(u * r, -a.limit), a.limit);
+    return g / (1.0f + expf(-a.slope * g)) * (u + a.shift);
+}
+
 #define RT_BM 64
 #define RT_BN 64
 #define RT_BK 16
@@ -149,7 +169,7 @@ template <typename T, bool ACT>
 __global__ void __launch_bounds__(256)
 expert_gemm_kernel(const T* __restrict__ a, const int* __restrict__ token_of_row, const T* __restrict__ w,
                    T* __restrict__ out, const int* __restrict__ offsets, const int* __restrict__ tile_first,
-                   int n_real, int N, int K) {
+                   int n_real, int N, int K, RtAct act, const float* __restrict__ row_scale) {
     __shared__ float as[RT_BK][RT_BM + 4];
     __shared__ float ws[RT_BK][RT_BN + 4];
     __shared__ float us[ACT ? RT_BK : 1][RT_BN + 4];
@@ -225,7 +245,7 @@ expert_gemm_kernel(const T* __restrict__ a, const int* __restrict__ token_of_row
             if (ACT) {
                 // the products are rounded to the activations' type first, as a separate product would leave them
                 const float g = ni_to_float(ni_from_float<T>(v)), u = ni_to_float(ni_from_float<T>(acu[i][j]));
-                v = g / (1.0f + expf(-g)) * u;
+                v = rt_act(g, u, act, row_scale ? row_scale[r] : 1.0f);
             }
             out[(size_t)r * N + n] = ni_from_float<T>(v);
         }
@@ -237,7 +257,7 @@ expert_gemm_kernel(const T* __restrict__ a, const int* __restrict__ token_of_row
 template <bool ACT>
 __global__ void expert_rows_kernel(const __nv_bfloat16* __restrict__ a, const __nv_bfloat16* __restrict__ w,
                                    __nv_bfloat16* __restrict__ out, const int* __restrict__ ids, int n_pairs, int top,
-                                   int gather, int n_real, int N, int K) {
+                                   int gather, int n_real, int N, int K, RtAct act, const float* __restrict__ row_scale) {
     const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
     const int p = blockIdx.y;
     if (warp >= N) return;
@@ -274,7 +294,7 @@ __global__ void expert_rows_kernel(const __nv_bfloat16* __restrict__ a, const __
         u = ni_warp_sum(u);
         g = __bfloat162float(__float2bfloat16_rn(g));
         u = __bfloat162float(__float2bfloat16_rn(u));
-        g = g / (1.0f + expf(-g)) * u;
+        g = rt_act(g, u, act, row_scale ? row_scale[p] : 1.0f);
     }
     if (lane == 0) out[(size_t)p * N + warp] = __float2bfloat16_rn(g);
 }
@@ -284,14 +304,15 @@ __global__ void expert_rows_kernel(const __nv_bfloat16* __restrict__ a, const __
 template <typename T>
 __global__ void combine_kernel(const T* __restrict__ z, const T* __restrict__ x, const int* __restrict__ ids,
                                const float* __restrict__ weights, const int* __restrict__ row_of_pair,
-                               float* __restrict__ y, int d, int top, int n_real, int all_experts) {
+                               float* __restrict__ y, int d, int top, int n_real, int all_experts, int unit_real,
+                               int accumulate) {
     const int t = blockIdx.x;
     for (int c = threadIdx.x; c < d; c += blockDim.x) {
-        float acc = 0.f;
+        float acc = accumulate ? y[(size_t)t * d + c] : 0.f;
         for (int j = 0; j < top; ++j) {
             const int p = t * top + j;
-            const float wgt = weights[p];
             const int e = ids[p];
+            const float wgt = (unit_real && e < n_real) ? 1.0f : weights[p];
             const int row = all_experts > 0 ? t * all_experts + e : (row_of_pair ? row_of_pair[p] : p);
             const float v = e >= n_real ? ni_to_float(x[(size_t)t * d + c]) : ni_to_float(z[(size_t)row * d + c]);
             acc = fmaf(wgt, v, acc);
@@ -306,7 +327,7 @@ template <typename T>
 __global__ void combine_add_normed_kernel(const T* __restrict__ z, const T* __restrict__ x, const int* __restrict__ ids,
                                           const float* __restrict__ weights, const int* __restrict__ row_of_pair,
                                           float* __restrict__ h, const float* __restrict__ gain, float eps, int d, int top,
-                                          int n_real, int all_experts) {
+                                          int n_real, int all_experts, int unit_real) {
     extern __shared__ float ys[];          // [d]
     __shared__ float scratch[32];
     const int t = blockIdx.x;
@@ -318,7 +339,7 @@ __global__ void combine_add_normed_kernel(const T* __restrict__ z, const T* __re
             const int e = ids[p];
             const int row = all_experts > 0 ? t * all_experts + e : (row_of_pair ? row_of_pair[p] : p);
             const float v = e >= n_real ? ni_to_float(x[(size_t)t * d + c]) : ni_to_float(z[(size_t)row * d + c]);
-            acc = fmaf(weights[p], v, acc);
+            acc = fmaf((unit_real && e < n_real) ? 1.0f : weights[p], v, acc);
         }
         ys[c] = acc;
         ss += acc * acc;
@@ -334,7 +355,7 @@ template <typename T>
 __global__ void combine_add_normed_vec_kernel(const T* __restrict__ z, const T* __restrict__ x, const int* __restrict__ ids,
                                               const float* __restrict__ weights, const int* __restrict__ row_of_pair,
                                               float* __restrict__ h, const float* __restrict__ gain, float eps, int d, int top,
-                                              int n_real, int all_experts) {
+                                              int n_real, int all_experts, int unit_real) {
     constexpr int V = NiVec16<T>::N;
     extern __shared__ __align__(16) float ys[];          // [d]
     __shared__ float scratch[32];
@@ -343,7 +364,7 @@ __global__ void combine_add_normed_vec_kernel(const T* __restrict__ z, const T* 
     const int t = blockIdx.x;
     for (int j = threadIdx.x; j < top; j += blockDim.x) {
         const int p = t * top + j, e = ids[p];
-        s_w[j] = weights[p];
+        s_w[j] = (unit_real && e < n_real) ? 1.0f : weights[p];
         s_row[j] = e >= n_real ? -1 : (all_experts > 0 ? t * all_experts + e : (row_of_pair ? row_of_pair[p] : p));
     }
     __syncthreads();
@@ -380,7 +401,7 @@ __global__ void combine_add_normed_vec_kernel(const T* __restrict__ z, const T* 
 
 NI_EXPORT int ni_route(const void* x, int dtype, const float* w_router, const float* bias, int* ids, float* weights,
                        int* counts, int n_tokens, int d, int n_all, int n_real, int top, int renormalize,
-                       cudaStream_t stream) {
+                       int sigmoid_scores, float* all_scores, cudaStream_t stream) {
     if (n_tokens <= 0) return NI_OK;
     if (d <= 0 || n_all <= 0 || n_real < 0 || n_real > n_all || top <= 0 || top > n_all) return NI_ERR_BAD_ARGUMENT;
     if (n_all > RT_MAX_EXPERTS || (renormalize && top > 32)) return NI_ERR_UNSUPPORTED_SIZE;
@@ -388,11 +409,13 @@ NI_EXPORT int ni_route(const void* x, int dtype, const float* w_router, const fl
     const size_t smem = (size_t)d * sizeof(float);
     if (dtype == NI_DTYPE_F32)
         route_kernel<float><<<n_tokens, RT_ROUTE_WARPS * 32, smem, stream>>>((const float*)x, w_router, bias, ids, weights,
-                                                                           counts, n_tokens, d, n_all, n_real, top, renormalize);
+                                                                           counts, n_tokens, d, n_all, n_real, top, renormalize,
+                                                                           sigmoid_scores, all_scores);
     else if (dtype == NI_DTYPE_BF16)
         route_kernel<__nv_bfloat16><<<n_tokens, RT_ROUTE_WARPS * 32, smem, stream>>>((const __nv_bfloat16*)x, w_router, bias,
                                                                                    ids, weights, counts, n_tokens, d, n_all,
-                                                                                   n_real, top, renormalize);
+                                                                                   n_real, top, renormalize, sigmoid_scores,
+                                                                                   all_scores);
     else
         return NI_ERR_BAD_ARGUMENT;
     NI_RETURN_LAUNCH_STATUS();
@@ -401,27 +424,29 @@ NI_EXPORT int ni_route(const void* x, int dtype, const float* w_router, const fl
 // counts [n_real] (zero before the route kernel ran, zero again afterwards), offsets and tile_first [n_real + 1],
 // cursor [n_real], row_of_pair [n_pairs], token_of_row [n_pairs]
 NI_EXPORT int ni_route_layout(const int* ids, int* counts, int* offsets, int* tile_first, int* cursor, int* row_of_pair,
-                              int* token_of_row, int n_pairs, int top, int n_real, cudaStream_t stream) {
+                              int* token_of_row, int n_pairs, int top, int n_real, const float* weights,
+                              float* weight_of_row, cudaStream_t stream) {
     if (n_pairs <= 0) return NI_OK;
     if (n_real < 0 || top <= 0) return NI_ERR_BAD_ARGUMENT;
     layout_kernel<<<1, 32, 0, stream>>>(counts, offsets, tile_first, cursor, n_real, RT_BM);
     scatter_kernel<<<(n_pairs + 255) / 256, 256, 0, stream>>>(ids, offsets, cursor, row_of_pair, token_of_row, n_pairs, top,
-                                                              n_real);
+                                                              n_real, weights, weight_of_row);
     NI_RETURN_LAUNCH_STATUS();
 }
 
 // act != 0: w is [n_real, 2 N, K] (gate rows, then up rows) and out = silu(gate) * up
 NI_EXPORT int ni_expert_gemm(const void* a, int dtype, const int* token_of_row, const void* w, void* out,
                              const int* offsets, const int* tile_first, int n_pairs, int n_real, int N, int K, int act,
-                             cudaStream_t stream) {
+                             float limit, float slope, float shift, const float* row_scale, cudaStream_t stream) {
     if (n_pairs <= 0 || n_real <= 0 || N <= 0) return NI_OK;
     if (K <= 0) return NI_ERR_BAD_ARGUMENT;
     const int max_tiles = (n_pairs + RT_BM - 1) / RT_BM + (n_real < n_pairs ? n_real : n_pairs);
     dim3 grid((N + RT_BN - 1) / RT_BN, max_tiles);
     if (grid.y > 65535) return NI_ERR_UNSUPPORTED_SIZE;
+    const RtAct ra = {limit, slope, shift};
 #define LAUNCH(T, ACT)                                                                                             \
     expert_gemm_kernel<T, ACT><<<grid, 256, 0, stream>>>((const T*)a, token_of_row, (const T*)w, (T*)out, offsets, \
-                                                         tile_first, n_real, N, K)
+                                                         tile_first, n_real, N, K, ra, row_scale)
     if (dtype == NI_DTYPE_F32) { if (act) LAUNCH(float, true); else LAUNCH(float, false); }
     else if (dtype == NI_DTYPE_BF16) { if (act) LAUNCH(__nv_bfloat16, true); else LAUNCH(__nv_bfloat16, false); }
     else return NI_ERR_BAD_ARGUMENT;
@@ -430,23 +455,25 @@ NI_EXPORT int ni_expert_gemm(const void* a, int dtype, const int* token_of_row, 
 }
 
 NI_EXPORT int ni_expert_rows(const void* a, const void* w, void* out, const int* ids, int n_pairs, int top, int gather,
-                             int n_real, int N, int K, int act, cudaStream_t stream) {
+                             int n_real, int N, int K, int act, float limit, float slope, float shift,
+                             const float* row_scale, cudaStream_t stream) {
     if (n_pairs <= 0 || n_real <= 0 || N <= 0) return NI_OK;
     if (K <= 0 || top <= 0) return NI_ERR_BAD_ARGUMENT;
     if (K % 8 || n_pairs > 65535) return NI_ERR_UNSUPPORTED_SIZE;
     dim3 grid((N + 7) / 8, n_pairs);
+    const RtAct ra = {limit, slope, shift};
     if (act)
         expert_rows_kernel<true><<<grid, 256, 0, stream>>>((const __nv_bfloat16*)a, (const __nv_bfloat16*)w,
-                                                           (__nv_bfloat16*)out, ids, n_pairs, top, gather, n_real, N, K);
+                                                           (__nv_bfloat16*)out, ids, n_pairs, top, gather, n_real, N, K, ra, row_scale);
     else
         expert_rows_kernel<false><<<grid, 256, 0, stream>>>((const __nv_bfloat16*)a, (const __nv_bfloat16*)w,
-                                                            (__nv_bfloat16*)out, ids, n_pairs, top, gather, n_real, N, K);
+                                                            (__nv_bfloat16*)out, ids, n_pairs, top, gather, n_real, N, K, ra, row_scale);
     NI_RETURN_LAUNCH_STATUS();
 }
 
 NI_EXPORT int ni_route_combine_add_normed(const void* z, const void* x, int dtype, const int* ids, const float* weights,
                                           const int* row_of_pair, float* h, const float* gain, float eps, int n_tokens,
-                                          int d, int top, int n_real, int all_experts, cudaStream_t stream) {
+                                          int d, int top, int n_real, int all_experts, int unit_real, cudaStream_t stream) {
     if (n_tokens <= 0) return NI_OK;
     if (d <= 0 || top <= 0) return NI_ERR_BAD_ARGUMENT;
     if (d > 12000) return NI_ERR_UNSUPPORTED_SIZE;
@@ -454,20 +481,20 @@ NI_EXPORT int ni_route_combine_add_normed(const void* z, const void* x, int dtyp
     const size_t smem = (size_t)d * sizeof(float);
     if (top <= RT_MAX_EXPERTS && dtype == NI_DTYPE_BF16 && d % 8 == 0) {
         combine_add_normed_vec_kernel<__nv_bfloat16><<<n_tokens, threads, smem, stream>>>(
-            (const __nv_bfloat16*)z, (const __nv_bfloat16*)x, ids, weights, row_of_pair, h, gain, eps, d, top, n_real, all_experts);
+            (const __nv_bfloat16*)z, (const __nv_bfloat16*)x, ids, weights, row_of_pair, h, gain, eps, d, top, n_real, all_experts, unit_real);
         NI_RETURN_LAUNCH_STATUS();
     }
     if (top <= RT_MAX_EXPERTS && dtype == NI_DTYPE_F32 && d % 4 == 0) {
         combine_add_normed_vec_kernel<float><<<n_tokens, threads, smem, stream>>>(
-            (const float*)z, (const float*)x, ids, weights, row_of_pair, h, gain, eps, d, top, n_real, all_experts);
+            (const float*)z, (const float*)x, ids, weights, row_of_pair, h, gain, eps, d, top, n_real, all_experts, unit_real);
         NI_RETURN_LAUNCH_STATUS();
     }
     if (dtype == NI_DTYPE_F32)
         combine_add_normed_kernel<float><<<n_tokens, threads, smem, stream>>>((const float*)z, (const float*)x, ids, weights,
-                                                                             row_of_pair, h, gain, eps, d, top, n_real, all_experts);
+                                                                             row_of_pair, h, gain, eps, d, top, n_real, all_experts, unit_real);
     else if (dtype == NI_DTYPE_BF16)
         combine_add_normed_kernel<__nv_bfloat16><<<n_tokens, threads, smem, stream>>>(
-            (const __nv_bfloat16*)z, (const __nv_bfloat16*)x, ids, weights, row_of_pair, h, gain, eps, d, top, n_real, all_experts);
+            (const __nv_bfloat16*)z, (const __nv_bfloat16*)x, ids, weights, row_of_pair, h, gain, eps, d, top, n_real, all_experts, unit_real);
     else
         return NI_ERR_BAD_ARGUMENT;
     NI_RETURN_LAUNCH_STATUS();
@@ -475,16 +502,17 @@ NI_EXPORT int ni_route_combine_add_normed(const void* z, const void* x, int dtyp
 
 NI_EXPORT int ni_route_combine(const void* z, const void* x, int dtype, const int* ids, const float* weights,
                                const int* row_of_pair, float* y, int n_tokens, int d, int top, int n_real,
-                               int all_experts, cudaStream_t stream) {
+                               int all_experts, int unit_real, int accumulate, cudaStream_t stream) {
     if (n_tokens <= 0) return NI_OK;
     if (d <= 0 || top <= 0) return NI_ERR_BAD_ARGUMENT;
     const int threads = d >= 1024 ? 256 : 128;
     if (dtype == NI_DTYPE_F32)
         combine_kernel<float><<<n_tokens, threads, 0, stream>>>((const float*)z, (const float*)x, ids, weights, row_of_pair, y,
-                                                               d, top, n_real, all_experts);
+                                                               d, top, n_real, all_experts, unit_real, accumulate);
     else if (dtype == NI_DTYPE_BF16)
         combine_kernel<__nv_bfloat16><<<n_tokens, threads, 0, stream>>>((const __nv_bfloat16*)z, (const __nv_bfloat16*)x, ids,
-                                                                       weights, row_of_pair, y, d, top, n_real, all_experts);
+                                                                       weights, row_of_pair, y, d, top, n_real, all_experts,
+                                                                       unit_real, accumulate);
     else
         return NI_ERR_BAD_ARGUMENT;
     NI_RETURN_LAUNCH_STATUS();

@@ -32,8 +32,13 @@ class DecoderModel:
             if hasattr(self.blocks[-1], "bind_embedding"):     # a block that reads a table the embedding owns
                 self.blocks[-1].bind_embedding(self.embedding)
         # vectors that join the stream before marked runs (LayerRun.stream_input): FP32 rows on the device
+        # ... or, with stream_input_kind "project_with_embedding", the matrix W of x <- W [x; x0] (compute dtype)
         self.stream_inputs = None
-        if config.stream_inputs > 0:
+        self.projects_stream = config.stream_inputs > 0 and config.stream_input_kind == "project_with_embedding"
+        if self.projects_stream:
+            self.stream_inputs = rt.weight(by_scope[("stream_inputs",)]["weight"])
+            self.kernel_modules = ("pointwise",)      # the library of csrc that holds the concatenating cast
+        elif config.stream_inputs > 0:
             self.stream_inputs = rt.gain(by_scope[("stream_inputs",)]["weight"])
         self.final_norm = registry.part("norm", config.final_norm.kind)(
             config.final_norm, d, by_scope.get(("final_norm",), {}), rt)
@@ -82,14 +87,28 @@ class DecoderModel:
         else:
             self.embedding.forward(ctx.tokens, h)
         delta = None
+        h0 = None
+        if self.projects_stream:
+            h0 = h                   # what the embedding produced stays as it is: the runs go on in a stream of their own
+            h = None
         for r, run in enumerate(cfg.schedule):
+            if h is None and run.stream_input is None:
+                h = h0.clone()       # runs before the first marked one
             if run.stream_input is not None:
                 # a vector joins the stream before this run; what the block before left pending goes in first
                 if delta is not None and not isinstance(delta, ops.NormHandoff):
                     ops.residual_add(h, delta)
                 delta = None
-                ops.add_row(h, self.stream_inputs[run.stream_input])
+                if self.projects_stream:
+                    # x <- W [x; x0]: both streams side by side in the compute dtype, one product, FP32 out
+                    both = rt.empty(ctx.n_tokens, 2 * cfg.hidden_size)
+                    ops.concat_cast(h if h is not None else h0, h0, both)
+                    h = rt.linear(both, self.stream_inputs, out_dtype=torch.float32)
+                else:
+                    ops.add_row(h, self.stream_inputs[run.stream_input])
             ctx.read_after, ctx.norm_after = self._read_after[r], self._norm_after[r]
             delta = self.blocks[run.layer].forward(h, delta, ctx, caches[r])
         ctx.read_after, ctx.norm_after = (), None
+        if h is None:
+            h = h0
         return self.head.forward(h, delta, self.final_norm, ctx)

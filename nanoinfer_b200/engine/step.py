@@ -208,7 +208,7 @@ class ModelRunner:
         bf16 = self.rt.dtype == torch.bfloat16
         needed = {"elementwise"} | ({"gemv_bf16", "gemv_ksplit"} if bf16 else {"gemm_f32"}) | ({"decode_fused"} if fused_decode else set())
         all_parts = [p for b in self.model.blocks for p in (b, getattr(b, "mixer", None), getattr(b, "feed_forward", None))] \
-            + [self.model.embedding, self.model.head]
+            + [self.model.embedding, self.model.head, self.model]
         for part in all_parts:
             if part is None:
                 continue

@@ -34,7 +34,7 @@ _SIGNATURES = {
         "ni_rope_kv_write": [_P, _I, _P, _P, _P, _P, _P, _P, _I, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P],
     },
     "attention_generic": {
-        "ni_attention_generic": [_P, _I, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _F, _P, _F, _P],
+        "ni_attention_generic": [_P, _I, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _F, _P, _F, _I, _P],
     },
     "gemm_f32": {
         "ni_gemm_f32": [_P, _P, _P, _I, _I, _I, _P],
@@ -49,19 +49,28 @@ _SIGNATURES = {
         "ni_add_row": [_P, _P, _I, _I, _I, _P],
         "ni_embedding_scaled": [_P, _P, _I, _F, _P, _I, _I, _I, _P],
         "ni_scale_f32": [_P, _F, _LL, _P],
-        "ni_capped_glu": [_P, _P, _I, _I, _I, _F, _F, _F, _P],
+        "ni_capped_glu": [_P, _P, _I, _I, _I, _F, _F, _F, _P, _P],
+        "ni_concat_cast": [_P, _P, _P, _I, _I, _I, _P],
+        "ni_relu_squared": [_P, _P, _I, _LL, _P],
+    },
+    "qk_norm_rope": {
+        "ni_qk_norm_rope": [_P, _I, _I, _P, _P, _P, _F, _P, _P, _P, _I, _P, _F, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P],
+    },
+    "lightning": {
+        "ni_lightning_recurrence": [_P, _I, _I, _P, _LL, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P],
+        "ni_lightning_gated_norm": [_P, _P, _I, _I, _I, _P, _F, _P, _I, _I, _P],
     },
     "conv_attention": {
         "ni_conv_qk_prepare": [_P, _I, _I, _P, _P, _P, _F, _P, _LL, _P, _P, _P, _P, _P, _I, _P, _P, _P, _P,
                                _I, _I, _I, _I, _I, _I, _I, _I, _P],
     },
     "routed": {
-        "ni_route": [_P, _I, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
-        "ni_route_layout": [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _P],
-        "ni_expert_gemm": [_P, _I, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P],
-        "ni_expert_rows": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P],
-        "ni_route_combine": [_P, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P],
-        "ni_route_combine_add_normed": [_P, _P, _I, _P, _P, _P, _P, _P, _F, _I, _I, _I, _I, _I, _P],
+        "ni_route": [_P, _I, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P, _P],
+        "ni_route_layout": [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _P, _P, _P],
+        "ni_expert_gemm": [_P, _I, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _F, _F, _P, _P],
+        "ni_expert_rows": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _F, _F, _F, _P, _P],
+        "ni_route_combine": [_P, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P],
+        "ni_route_combine_add_normed": [_P, _P, _I, _P, _P, _P, _P, _P, _F, _I, _I, _I, _I, _I, _I, _P],
     },
     "delta_rule": {
         "ni_delta_prepare": [_P, _P, _P, _P, _P, _LL, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P, _P],
@@ -331,20 +340,24 @@ def attention_generic(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Ten
                       block_table: torch.Tensor, n_q_heads: int, n_kv_heads: int, head_dim: int,
                       page_size: int, window: Optional[int], scale: float,
                       token_list: Optional[torch.Tensor] = None, head_slopes: Optional[torch.Tensor] = None,
-                      score_cap: float = 0.0) -> None:
+                      score_cap: float = 0.0, value_dim: Optional[int] = None) -> None:
     """The plain attention kernel (any dtype, any head size up to 512).  ``token_list``
     int32 [n] restricts it to those tokens of the step.  ``head_slopes`` float32 [Hq] adds
     slope[h] * (key position - query position) to the scaled scores of head h.  ``score_cap`` c > 0
-    bounds the scaled scores: s <- c * tanh(s / c)."""
+    bounds the scaled scores: s <- c * tanh(s / c).  ``value_dim``: the size of a value where it differs
+    from the keys' (value pages [P, Hkv, page_size, value_dim], out [T, Hq * value_dim])."""
     if head_slopes is not None and head_slopes.numel() != n_q_heads:
         raise KernelError("attention: one slope per query head")
     n = q.shape[0]
-    if q.shape != (n, n_q_heads * head_dim) or out.shape != q.shape:
-        raise KernelError("attention: q and out must be [T, Hq * head_dim]")
+    v_dim = head_dim if value_dim is None else int(value_dim)
+    if q.shape != (n, n_q_heads * head_dim) or out.shape != (n, n_q_heads * v_dim):
+        raise KernelError("attention: q must be [T, Hq * head_dim] and out [T, Hq * value_dim]")
     if not (q.dtype == out.dtype == k_pages.dtype == v_pages.dtype):
         raise KernelError("attention: all operands must share one dtype")
-    if head_dim > 512:
-        raise KernelError(f"attention: head_dim {head_dim} > 512 is not supported")
+    if head_dim > 512 or v_dim > 512 or v_dim <= 0:
+        raise KernelError(f"attention: head_dim {head_dim} or value_dim {v_dim} beyond 512 is not supported")
+    if k_pages.shape[-1] != head_dim or v_pages.shape[-1] != v_dim:
+        raise KernelError("attention: the pages' rows must have the keys' and the values' sizes")
     _check(load("attention_generic").ni_attention_generic(
         _dev(q, "q"), _code(q, "q"), _dev(k_pages, "k_pages"), _dev(v_pages, "v_pages"),
         _dev(out, "out"), _dev(token_list, "token_list", torch.int32) if token_list is not None else None,
@@ -353,7 +366,7 @@ def attention_generic(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Ten
         block_table.shape[1], n if token_list is None else token_list.numel(), n_q_heads, n_kv_heads, head_dim, page_size,
         int(window) if window else 0, float(scale),
         _dev(head_slopes, "head_slopes", torch.float32) if head_slopes is not None else None, float(score_cap),
-        _stream()), "attention_generic")
+        v_dim, _stream()), "attention_generic")
 
 
 def gemm_f32(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
@@ -522,14 +535,94 @@ def scale_f32(x: torch.Tensor, factor: float) -> None:
     _check(load("pointwise").ni_scale_f32(_dev(x, "x", torch.float32), float(factor), x.numel(), _stream()), "scale_f32")
 
 
-def capped_glu(gate_up: torch.Tensor, out: torch.Tensor, limit: float, slope: float, shift: float) -> None:
-    """out = g * sigmoid(slope * g) * (u + shift) with g = min(gate, limit), u = clamp(up, -limit, limit);
-    gate_up = [gate | up] [T, 2I], out [T, I], one dtype."""
+def capped_glu(gate_up: torch.Tensor, out: torch.Tensor, limit: float, slope: float, shift: float,
+               row_scale: Optional[torch.Tensor] = None) -> None:
+    """out = g * sigmoid(slope * g) * (u + shift) with g = min(r gate, limit), u = clamp(r up, -limit, limit);
+    gate_up = [gate | up] [T, 2I], out [T, I], one dtype; ``row_scale`` float32 [T]: r per row (else 1) - what the
+    unit computes when its input was multiplied by r."""
     n, inter = out.shape
-    if gate_up.shape != (n, 2 * inter) or gate_up.dtype != out.dtype:
-        raise KernelError("capped_glu: gate_up must be [T, 2I] of out's dtype")
+    if gate_up.shape != (n, 2 * inter) or gate_up.dtype != out.dtype or (row_scale is not None and row_scale.numel() != n):
+        raise KernelError("capped_glu: gate_up must be [T, 2I] of out's dtype (and row_scale [T])")
     _check(load("pointwise").ni_capped_glu(_dev(gate_up, "gate_up"), _dev(out, "out"), _code(out, "out"), n, inter,
-                                           float(limit), float(slope), float(shift), _stream()), "capped_glu")
+                                           float(limit), float(slope), float(shift),
+                                           _dev(row_scale, "row_scale", torch.float32) if row_scale is not None else None,
+                                           _stream()), "capped_glu")
+
+
+def concat_cast(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor) -> None:
+    """out[t] = [a[t] | b[t]] in out's dtype; a, b float32 [T, d], out [T, 2d]."""
+    n, d = a.shape
+    if b.shape != a.shape or out.shape != (n, 2 * d):
+        raise KernelError("concat_cast: shapes do not agree")
+    _check(load("pointwise").ni_concat_cast(_dev(a, "a", torch.float32), _dev(b, "b", torch.float32), _dev(out, "out"),
+                                            _code(out, "out"), n, d, _stream()), "concat_cast")
+
+
+def relu_squared(z: torch.Tensor, out: torch.Tensor) -> None:
+    """out = max(z, 0)^2 element by element; one dtype."""
+    if z.shape != out.shape or z.dtype != out.dtype:
+        raise KernelError("relu_squared: shapes or dtypes do not agree")
+    _check(load("pointwise").ni_relu_squared(_dev(z, "z"), _dev(out, "out"), _code(out, "out"), z.numel(), _stream()),
+           "relu_squared")
+
+
+def qk_norm_rope(qkv, bias, q_gain, k_gain, eps, positions, seq_of_token, block_table, inv_freq, magnitude, q_out,
+                 k_pages, v_pages, n_heads, n_kv_heads, head_dim, value_dim, rotary_dim, page_size) -> None:
+    """From the fused projection ``qkv`` [T, ld] (columns q | k | v): + ``bias`` (float32 over those columns, or
+    None); RMS norm of all the row's query values together and of all its key values together (``q_gain`` float32
+    [H hd], ``k_gain`` float32 [Hkv hd]; both None: no norm); rotation of the first ``rotary_dim`` dimensions of every
+    head, dimension i paired with i + rotary_dim / 2, cosine and sine times ``magnitude``; queries -> q_out [T, H hd],
+    keys -> k_pages [P, Hkv, page_size, hd], values -> v_pages [P, Hkv, page_size, value_dim] (None: nothing written)."""
+    n = qkv.shape[0]
+    f32, i32 = torch.float32, torch.int32
+    cols = (n_heads + n_kv_heads) * head_dim + n_kv_heads * value_dim
+    write = k_pages is not None
+    if qkv.shape[1] < cols or q_out.shape != (n, n_heads * head_dim) or q_out.dtype != qkv.dtype:
+        raise KernelError("qk_norm_rope: shapes or dtypes do not agree")
+    if write and (tuple(k_pages.shape[1:]) != (n_kv_heads, page_size, head_dim) or k_pages.dtype != qkv.dtype
+                  or tuple(v_pages.shape[1:]) != (n_kv_heads, page_size, value_dim) or v_pages.dtype != qkv.dtype):
+        raise KernelError("qk_norm_rope: pages must be [P, Hkv, page_size, head_dim] and [P, Hkv, page_size, value_dim]")
+    if (bias is not None and bias.numel() != cols) or (q_gain is None) != (k_gain is None) or \
+            (q_gain is not None and (q_gain.numel() != n_heads * head_dim or k_gain.numel() != n_kv_heads * head_dim)):
+        raise KernelError("qk_norm_rope: the bias or a gain has another size")
+    if rotary_dim > 0 and inv_freq.numel() != rotary_dim // 2:
+        raise KernelError("qk_norm_rope: inv_freq must have rotary_dim / 2 entries")
+    _check(load("qk_norm_rope").ni_qk_norm_rope(
+        _dev(qkv, "qkv"), _code(qkv, "qkv"), qkv.shape[1], _dev(bias, "bias", f32) if bias is not None else None,
+        _dev(q_gain, "q_gain", f32) if q_gain is not None else None, _dev(k_gain, "k_gain", f32) if k_gain is not None else None,
+        float(eps), _dev(positions, "positions", i32), _dev(seq_of_token, "seq_of_token", i32),
+        _dev(block_table, "block_table", i32), block_table.shape[1], _dev(inv_freq, "inv_freq", f32), float(magnitude),
+        _dev(q_out, "q_out"), _dev(k_pages, "k_pages") if write else None, _dev(v_pages, "v_pages") if write else None,
+        n, n_heads, n_kv_heads, head_dim, value_dim, rotary_dim, page_size, _stream()), "qk_norm_rope")
+
+
+LIGHTNING_MAX_DIM = 256      # the largest key size whose chunk buffers fit a block's shared memory
+
+
+def lightning_recurrence(proj, state, cu_q, slots, n_seqs, decay, n_heads, dim, vdim, out) -> None:
+    """Linear attention with a decay per head over a step's tokens, request by request: with q, k [H, dim] and v
+    [H, vdim] = silu of proj's columns (q | k | v | ...), S <- decay_h S + k v^T and out = S^T q, all float32;
+    ``state`` float32 [slots, >= H dim vdim] holds every request's S and advances by the step's tokens; out float32
+    [T, H vdim]."""
+    n = proj.shape[0]
+    if proj.shape[1] < n_heads * (2 * dim + vdim) or out.shape != (n, n_heads * vdim) or decay.numel() != n_heads \
+            or state.shape[1] < n_heads * dim * vdim:
+        raise KernelError("lightning_recurrence: shapes do not agree")
+    _check(load("lightning").ni_lightning_recurrence(
+        _dev(proj, "proj"), _code(proj, "proj"), proj.shape[1], _dev(state, "state", torch.float32), state.shape[1],
+        _dev(cu_q, "cu_q", torch.int32), _dev(slots, "slots", torch.int32), _dev(decay, "decay", torch.float32),
+        _dev(out, "out", torch.float32), n, n_seqs, n_heads, dim, vdim, _stream()), "lightning_recurrence")
+
+
+def lightning_gated_norm(o, proj, col0, weight, eps, y) -> None:
+    """y = o / sqrt(mean(o^2) + eps) * weight * sigmoid(proj[:, col0 : col0 + N]) row by row; o float32 [T, N], weight
+    float32 [N], y [T, N] of proj's dtype."""
+    n, width = o.shape
+    if y.shape != o.shape or y.dtype != proj.dtype or weight.numel() != width or proj.shape[0] != n:
+        raise KernelError("lightning_gated_norm: shapes or dtypes do not agree")
+    _check(load("lightning").ni_lightning_gated_norm(
+        _dev(o, "o", torch.float32), _dev(proj, "proj"), _code(proj, "proj"), proj.shape[1], int(col0),
+        _dev(weight, "weight", torch.float32), float(eps), _dev(y, "y"), n, width, _stream()), "lightning_gated_norm")
 
 
 def conv_qk_prepare(proj, conv_w, q_gain, k_gain, eps, state, positions, seq_of_token, cu_q, slots, n_seqs, block_table,
@@ -567,8 +660,11 @@ def conv_qk_prepare(proj, conv_w, q_gain, k_gain, eps, state, positions, seq_of_
 ROUTE_MAX_EXPERTS = 256      # what the routing kernel keeps in shared memory per token
 
 
-def route(x, w_router, bias, ids, weights, counts, n_real, top, renormalize=False) -> None:
-    """Per token: scores = softmax(w_router x) (float32; w_router float32 [E, d]); the ``top`` experts with the
+def route(x, w_router, bias, ids, weights, counts, n_real, top, renormalize=False, sigmoid_scores=False,
+          all_scores=None) -> None:
+    """Per token: scores = softmax(w_router x), or with ``sigmoid_scores`` sigmoid(w_router x), each expert on its own
+    (float32; w_router float32 [E, d]); ``all_scores`` float32 [T, n_real] (or None) receives every real expert's score;
+    the ``top`` experts with the
     largest score + bias (``bias`` float32 [E] or None) -> ids int32 [T, top], their scores -> weights float32
     [T, top] (divided by their sum if ``renormalize``).  ``counts`` int32 [n_real] (or None) receives how many
     tokens chose each of the first ``n_real`` experts (added to what it holds)."""
@@ -582,13 +678,17 @@ def route(x, w_router, bias, ids, weights, counts, n_real, top, renormalize=Fals
                                    _dev(bias, "bias", torch.float32) if bias is not None else None,
                                    _dev(ids, "ids", torch.int32), _dev(weights, "weights", torch.float32),
                                    _dev(counts, "counts", torch.int32) if counts is not None else None, n, d, e, n_real, top,
-                                   1 if renormalize else 0, _stream()), "route")
+                                   1 if renormalize else 0, 1 if sigmoid_scores else 0,
+                                   _dev(all_scores, "all_scores", torch.float32) if all_scores is not None else None,
+                                   _stream()), "route")
 
 
-def route_layout(ids, counts, offsets, tile_first, cursor, row_of_pair, token_of_row, n_real) -> None:
+def route_layout(ids, counts, offsets, tile_first, cursor, row_of_pair, token_of_row, n_real, weights=None,
+                 weight_of_row=None) -> None:
     """Lay the (token, choice) pairs out expert by expert: offsets / tile_first int32 [n_real + 1] (first row and
     first 64-row tile of each expert's stretch), row_of_pair int32 [T top] (-1 for pairs of identity experts),
-    token_of_row int32 [T top]; counts comes from route() and is left zero, cursor int32 [n_real] is scratch."""
+    token_of_row int32 [T top]; counts comes from route() and is left zero, cursor int32 [n_real] is scratch.
+    With ``weights`` (route's) and ``weight_of_row`` float32 [T top], every row also receives its pair's weight."""
     n, top = ids.shape
     i32 = torch.int32
     if offsets.numel() < n_real + 1 or tile_first.numel() < n_real + 1 or row_of_pair.numel() < n * top or token_of_row.numel() < n * top:
@@ -596,13 +696,20 @@ def route_layout(ids, counts, offsets, tile_first, cursor, row_of_pair, token_of
     _check(load("routed").ni_route_layout(_dev(ids, "ids", i32), _dev(counts, "counts", i32), _dev(offsets, "offsets", i32),
                                           _dev(tile_first, "tile_first", i32), _dev(cursor, "cursor", i32),
                                           _dev(row_of_pair, "row_of_pair", i32), _dev(token_of_row, "token_of_row", i32),
-                                          n * top, top, n_real, _stream()), "route_layout")
+                                          n * top, top, n_real,
+                                          _dev(weights, "weights", torch.float32) if weight_of_row is not None else None,
+                                          _dev(weight_of_row, "weight_of_row", torch.float32) if weight_of_row is not None else None,
+                                          _stream()), "route_layout")
 
 
-def expert_gemm(a, token_of_row, w, out, offsets, tile_first, n_pairs, act: bool) -> None:
+PLAIN_GLU = (float("inf"), 1.0, 0.0)      # (limit, slope, shift) of silu(gate) * up
+
+
+def expert_gemm(a, token_of_row, w, out, offsets, tile_first, n_pairs, act: bool, glu=PLAIN_GLU, row_scale=None) -> None:
     """out[row] = a[row] . w[e]^T for the rows of every expert e's stretch (``token_of_row`` given: a[token of the
-    row]); w [E, N, K], or with ``act`` [E, 2N, K] (gate rows, then up rows) and out = silu(gate) * up.  Each output
-    element is one ascending chain of FP32 fused multiply-adds."""
+    row]); w [E, N, K], or with ``act`` [E, 2N, K] (gate rows, then up rows) and out = the gated unit's activation
+    with ``glu`` = (limit, slope, shift) and ``row_scale`` float32 [rows] (see capped_glu; the default is silu(gate) *
+    up).  Each output element is one ascending chain of FP32 fused multiply-adds."""
     e, wn, k = w.shape
     n = wn // 2 if act else wn
     if a.shape[1] != k or out.shape[1] != n or out.shape[0] < n_pairs or a.dtype != w.dtype or out.dtype != w.dtype:
@@ -611,13 +718,15 @@ def expert_gemm(a, token_of_row, w, out, offsets, tile_first, n_pairs, act: bool
                                          _dev(token_of_row, "token_of_row", torch.int32) if token_of_row is not None else None,
                                          _dev(w, "w"), _dev(out, "out"), _dev(offsets, "offsets", torch.int32),
                                          _dev(tile_first, "tile_first", torch.int32), n_pairs, e, n, k, 1 if act else 0,
+                                         float(glu[0]), float(glu[1]), float(glu[2]),
+                                         _dev(row_scale, "row_scale", torch.float32) if row_scale is not None else None,
                                          _stream()), "expert_gemm")
 
 
 EXPERT_ROWS_MAX_PAIRS = 64      # (token, choice) pairs up to which a step takes the kernel with one warp per output
 
 
-def expert_rows(a, w, out, ids, gather: bool, act: bool) -> None:
+def expert_rows(a, w, out, ids, gather: bool, act: bool, glu=PLAIN_GLU, row_scale=None) -> None:
     """A few rows, bfloat16: out[p] = a[p or p / top] . w[ids[p]]^T for every pair p of a real expert (others are
     skipped), one warp per output; ``act`` as in expert_gemm.  K must be a multiple of 8."""
     e, wn, k = w.shape
@@ -627,13 +736,18 @@ def expert_rows(a, w, out, ids, gather: bool, act: bool) -> None:
     if a.shape[1] != k or out.shape != (n_pairs, n) or a.shape[0] != (n_pairs // top if gather else n_pairs):
         raise KernelError("expert_rows: shapes do not agree")
     _check(load("routed").ni_expert_rows(_dev(a, "a", bf), _dev(w, "w", bf), _dev(out, "out", bf), _dev(ids, "ids", torch.int32),
-                                         n_pairs, top, 1 if gather else 0, e, n, k, 1 if act else 0, _stream()), "expert_rows")
+                                         n_pairs, top, 1 if gather else 0, e, n, k, 1 if act else 0,
+                                         float(glu[0]), float(glu[1]), float(glu[2]),
+                                         _dev(row_scale, "row_scale", torch.float32) if row_scale is not None else None,
+                                         _stream()), "expert_rows")
 
 
-def route_combine(z, x, ids, weights, row_of_pair, y, n_real, all_experts: int = 0) -> None:
+def route_combine(z, x, ids, weights, row_of_pair, y, n_real, all_experts: int = 0, unit_real: bool = False,
+                  accumulate: bool = False) -> None:
     """y[t] = sum_j weights[t, j] * (z[row of pair (t, j)] for a real expert, x[t] for an identity expert), in the
     order of the choices, float32; row_of_pair None: pair p's row is p; ``all_experts`` = E > 0: z holds a row
-    for every (token, expert), [T E, d], and the pair's row is t E + its expert."""
+    for every (token, expert), [T E, d], and the pair's row is t E + its expert.  ``unit_real``: real experts' rows
+    count with weight 1 (their weight went into their input); ``accumulate``: the sum is added to what y holds."""
     n, top = ids.shape
     d = x.shape[1]
     if y.shape != (n, d) or z.shape[1] != d or z.dtype != x.dtype:
@@ -641,11 +755,13 @@ def route_combine(z, x, ids, weights, row_of_pair, y, n_real, all_experts: int =
     _check(load("routed").ni_route_combine(_dev(z, "z"), _dev(x, "x"), _code(x, "x"), _dev(ids, "ids", torch.int32),
                                            _dev(weights, "weights", torch.float32),
                                            _dev(row_of_pair, "row_of_pair", torch.int32) if row_of_pair is not None else None,
-                                           _dev(y, "y", torch.float32), n, d, top, n_real, int(all_experts), _stream()),
+                                           _dev(y, "y", torch.float32), n, d, top, n_real, int(all_experts),
+                                           1 if unit_real else 0, 1 if accumulate else 0, _stream()),
            "route_combine")
 
 
-def route_combine_add_normed(z, x, ids, weights, row_of_pair, h, gain, eps, n_real, all_experts: int = 0) -> None:
+def route_combine_add_normed(z, x, ids, weights, row_of_pair, h, gain, eps, n_real, all_experts: int = 0,
+                             unit_real: bool = False) -> None:
     """h[t] += y / sqrt(mean(y^2) + eps) * gain with y the sum that route_combine computes; h float32 [T, d]."""
     n, top = ids.shape
     d = x.shape[1]
@@ -654,8 +770,8 @@ def route_combine_add_normed(z, x, ids, weights, row_of_pair, h, gain, eps, n_re
     _check(load("routed").ni_route_combine_add_normed(
         _dev(z, "z"), _dev(x, "x"), _code(x, "x"), _dev(ids, "ids", torch.int32), _dev(weights, "weights", torch.float32),
         _dev(row_of_pair, "row_of_pair", torch.int32) if row_of_pair is not None else None, _dev(h, "h", torch.float32),
-        _dev(gain, "gain", torch.float32), float(eps), n, d, top, n_real, int(all_experts), _stream()),
-        "route_combine_add_normed")
+        _dev(gain, "gain", torch.float32), float(eps), n, d, top, n_real, int(all_experts), 1 if unit_real else 0,
+        _stream()), "route_combine_add_normed")
 
 
 GEMV_MAX_ROWS = 16      # what the skinny kernels take

@@ -12,7 +12,8 @@ from .base import WeightSlot
 
 
 class PreNormBlock:
-    """h += mixer(norm1(h)); h += ffn(norm2(h))  (src/model/llama.cpp:324-379).
+    """h += mixer(norm1(h)); h += ffn(norm2(h))  (src/model/llama.cpp:324-379).  A layer may have no
+    feed-forward (and then no second norm): it is the first half alone.
 
     The residual stream h is FP32 and updated in place.  Each addition is fused into the
     norm that follows it, so a block takes the addition still pending from the block before
@@ -26,10 +27,14 @@ class PreNormBlock:
             layer_spec.mixer_norm, hidden_size, weights_of("mixer_norm"), rt)
         self.mixer = part("mixer", layer_spec.mixer.kind)(
             layer_spec.mixer, hidden_size, weights_of("mixer"), rt)
-        self.ffn_norm = part("norm", layer_spec.ffn_norm.kind)(
-            layer_spec.ffn_norm, hidden_size, weights_of("ffn_norm"), rt)
-        self.feed_forward = part("feed_forward", layer_spec.feed_forward.kind)(
-            layer_spec.feed_forward, hidden_size, weights_of("feed_forward"), rt)
+        self.ffn_norm = self.feed_forward = None
+        if layer_spec.feed_forward is not None:
+            if layer_spec.ffn_norm is None:
+                raise ValueError("a pre-norm layer's feed-forward needs its norm")
+            self.ffn_norm = part("norm", layer_spec.ffn_norm.kind)(
+                layer_spec.ffn_norm, hidden_size, weights_of("ffn_norm"), rt)
+            self.feed_forward = part("feed_forward", layer_spec.feed_forward.kind)(
+                layer_spec.feed_forward, hidden_size, weights_of("feed_forward"), rt)
 
     def weights_in_order(self) -> tuple:
         return tuple(getattr(self.mixer, "weights_in_order", tuple)()) + tuple(getattr(self.feed_forward, "weights_in_order", tuple)())
@@ -58,6 +63,8 @@ class PreNormBlock:
             a = self._mix(h, delta, pre, ctx, cache, n, to_ffn)
         finally:
             ctx.read_after = after
+        if ffn is None:
+            return a                                 # the mixer's addition, pending or made
         then = ctx.norm_after if getattr(ffn, "hands_off_norm", False) else None
         if isinstance(a, NormHandoff):
             return ffn.forward_prenormed(a, ctx, residual=h, then_norm=then)

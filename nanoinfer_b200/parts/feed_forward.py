@@ -179,6 +179,48 @@ class CappedGLU(Part):
         return rt.linear(act, self.w_down, out_dtype=torch.float32)
 
 
+class SquaredReLU(Part):
+    """y = W_down relu(W_up x)^2: one up projection, the square of its positive part, one down projection."""
+
+    kernel_modules = ("pointwise",)       # libraries of csrc that this part's kernels live in
+
+    adds_into_residual = True
+    graph_safe = "all"
+
+    @staticmethod
+    def weight_slots(spec, hidden_size: int) -> Dict[str, WeightSlot]:
+        i = spec.intermediate_size
+        return {"up": WeightSlot((i, hidden_size)), "down": WeightSlot((hidden_size, i))}
+
+    def __init__(self, spec, hidden_size, weights, rt) -> None:
+        super().__init__(spec, hidden_size, weights, rt)
+        self.inter = spec.intermediate_size
+        self.w_up = rt.weight(weights["up"])
+        self.w_down = rt.weight(weights["down"])
+
+    def weights_in_order(self) -> tuple:
+        return (self.w_up, self.w_down)
+
+    def can_fuse_norm(self, norm, n_rows: int) -> bool:
+        return self.rt.skinny(n_rows, self.hidden_size) and self.rt.fuses_norm(norm)
+
+    def forward(self, x: torch.Tensor, ctx, residual=None):
+        return self.finish(self.rt.linear(x, self.w_up), ctx, residual=residual)
+
+    def forward_fused_norm(self, h: torch.Tensor, norm, ctx, residual=None):
+        """As forward, with x = norm(h): the norm runs inside the up projection (steps of a few rows)."""
+        return self.finish(self.project(h, norm), ctx, residual=residual)
+
+    def project(self, h: torch.Tensor, norm) -> torch.Tensor:
+        z = self.rt.empty(h.shape[0], self.inter)
+        ops.gemv_norm_bf16(h, norm.gain, norm.eps, None, self.w_up, z, ops.STORE_BF16)
+        return z
+
+    def finish(self, z: torch.Tensor, ctx, residual=None):
+        ops.relu_squared(z, z)
+        return self.rt.linear(z, self.w_down, out_dtype=torch.float32, residual=residual)
+
+
 class RoutedExperts(Part):
     """A routed feed-forward: ``experts`` small gated units W_down (silu(W_gate x) * (W_up x)) without biases, of
     which every token uses ``top``, plus ``identity_experts`` experts whose output is x itself (they have no
@@ -319,3 +361,4 @@ register_part("feed_forward", "swiglu", SwiGLU, replace=True)
 register_part("feed_forward", "capped_glu", CappedGLU, replace=True)
 register_part("feed_forward", "routed_experts", RoutedExperts, replace=True)
 register_part("feed_forward", "polynorm", PolyNorm, replace=True)
+register_part("feed_forward", "relu2", SquaredReLU, replace=True)

@@ -414,6 +414,123 @@ class ConvKeyAttention(PagedAttendMixin, Part):
         return rt.linear(att, self.w_o, out_dtype=torch.float32)
 
 
+class NormedQKAttention(PagedAttendMixin, Part):
+    """Grouped-query attention whose queries and keys are normed as a WHOLE.  With x the mixer's input:
+
+        q = W_q x + b_q,  k = W_k x + b_k,  v = W_v x + b_v     (the biases only with ``bias`` in the spec's extra)
+        q <- q / sqrt(mean(q^2) + eps) * w_q                    one RMS norm over all ``num_heads * head_dim`` query
+        k <- k / sqrt(mean(k^2) + eps) * w_k                    values, one over all key values, before the heads are
+                                                                split (only with ``qk_norm``; eps = ``norm_eps``)
+        q, k <- the position encoding                           (rotary: pairs (i, i + rotary_dim / 2) of the first
+                                                                ``rotary_dim`` dimensions of every head; the encoding's
+                                                                ``magnitude`` multiplies cosine and sine)
+        s = (q . k) softmax_scale;  causal softmax;  sum p v;   then W_o on the heads side by side
+
+    Keys have ``head_dim`` entries, values ``value_dim`` (the same unless the extra says otherwise).  The three
+    projections are one product; bias, both norms, the rotation and the cache write are one kernel
+    (csrc/qk_norm_rope.cu), FP32 inside whatever the tensors' type.  With values of the keys' size the attention
+    runs on the package's paged kernels (tcgen05 flash attention for prompt portions, split-K for single tokens);
+    other value sizes take the plain kernel, which knows them."""
+
+    kernel_modules = ("qk_norm_rope",)       # libraries of csrc that this part's kernels live in
+    kernel_modules_bf16 = ("attention_prefill_tc",)
+
+    adds_into_residual = True
+    graph_safe = "all"
+
+    @staticmethod
+    def _dims(spec):
+        e = spec.extra_dict()
+        return (spec.num_heads, spec.num_kv_heads, spec.head_dim, int(e.get("value_dim", spec.head_dim)),
+                bool(e.get("bias", False)), bool(e.get("qk_norm", True)))
+
+    @staticmethod
+    def weight_slots(spec, hidden_size: int) -> Dict[str, WeightSlot]:
+        h, g, d, v, bias, qk_norm = NormedQKAttention._dims(spec)
+        slots = {"q": WeightSlot((h * d, hidden_size)), "k": WeightSlot((g * d, hidden_size)),
+                 "v": WeightSlot((g * v, hidden_size))}
+        if bias:
+            slots.update({"q.b": WeightSlot((h * d,)), "k.b": WeightSlot((g * d,)), "v.b": WeightSlot((g * v,))})
+        if qk_norm:
+            slots.update({"q.norm": WeightSlot((h * d,), init="ones"), "k.norm": WeightSlot((g * d,), init="ones")})
+        slots["o"] = WeightSlot((hidden_size, h * v))
+        return slots
+
+    def __init__(self, spec, hidden_size, weights, rt) -> None:
+        Part.__init__(self, spec, hidden_size, weights, rt)
+        h, g, d, v, bias, qk_norm = self._dims(spec)
+        if h <= 0 or g <= 0 or h % g:
+            raise ConfigError("normed-qk attention: heads must be a positive multiple of kv_heads")
+        if not 0 < d <= 512 or not 0 < v <= 512:
+            raise ConfigError(f"normed-qk attention: key size {d} and value size {v} must lie in 1 .. 512")
+        if spec.window is not None:
+            raise ConfigError("normed-qk attention sees every earlier key (no window)")
+        self.n_heads, self.n_kv, self.head_dim, self.value_dim = h, g, d, v
+        self.window = None
+        self.scale = float(spec.softmax_scale)
+        self.eps = float(spec.extra_dict().get("norm_eps", 1e-6))
+        self.position = part("position", spec.position.kind)(spec.position, hidden_size, {}, rt)
+        if self.position.rotary_dim > d or (self.position.rotary_dim > 0 and self.position.interleaved):
+            raise ConfigError("normed-qk attention rotates the pairs (i, i + rotary_dim / 2) of at most head_dim dimensions")
+        if getattr(self.position, "head_slopes", None) is not None:
+            raise ConfigError("normed-qk attention takes no position encoding that acts on the scores")
+        self.magnitude = float(getattr(self.position, "magnitude", 1.0))
+        self.inv_freq = self.position.inv_freq if self.position.rotary_dim > 0 else \
+            torch.zeros(0, dtype=torch.float32, device=rt.device)
+        self.cols = (h + g) * d + g * v
+        rows = [weights["q"], weights["k"], weights["v"]]
+        pad = -self.cols % 8                      # zero rows, so that every row of the result starts on 16 bytes
+        if pad:
+            rows.append(torch.zeros(pad, hidden_size, dtype=weights["q"].dtype, device=weights["q"].device))
+        self.w_qkv = rt.weight(torch.cat(rows, dim=0))
+        self.w_o = rt.weight(weights["o"])
+        self.bias = rt.gain(torch.cat([weights["q.b"], weights["k.b"], weights["v.b"]])) if bias else None
+        self.q_gain = rt.gain(weights["q.norm"]) if qk_norm else None
+        self.k_gain = rt.gain(weights["k.norm"]) if qk_norm else None
+
+    def cache_need(self):
+        if self.value_dim == self.head_dim:
+            return PagedKVNeed(self.n_kv, self.head_dim, None)
+        return PagedNeed((("k", (self.n_kv, self.head_dim)), ("v", (self.n_kv, self.value_dim))), None)
+
+    def weights_in_order(self) -> tuple:
+        return (self.w_qkv, self.w_o)
+
+    def can_fuse_norm(self, norm, n_rows: int) -> bool:
+        return self.rt.skinny(n_rows, self.hidden_size) and self.rt.fuses_norm(norm)
+
+    def forward(self, x: torch.Tensor, ctx, cache, residual=None):
+        return self.finish(self.rt.linear(x, self.w_qkv), ctx, cache, residual=residual)
+
+    def forward_fused_norm(self, h: torch.Tensor, norm, ctx, cache, residual=None):
+        """As forward, with x = norm(h): the norm runs inside the projection (steps of a few rows)."""
+        return self.finish(self.project(h, norm), ctx, cache, residual=residual)
+
+    def project(self, h: torch.Tensor, norm) -> torch.Tensor:
+        qkv = self.rt.empty(h.shape[0], self.w_qkv.shape[0])
+        ops.gemv_norm_bf16(h, norm.gain, norm.eps, None, self.w_qkv, qkv, ops.STORE_BF16)
+        return qkv
+
+    def finish(self, qkv: torch.Tensor, ctx, cache, residual=None):
+        rt = self.rt
+        n = qkv.shape[0]
+        h, g, d, v = self.n_heads, self.n_kv, self.head_dim, self.value_dim
+        table = ctx.block_tables[cache.group]
+        q = rt.empty(n, h * d)
+        ops.qk_norm_rope(qkv, self.bias, self.q_gain, self.k_gain, self.eps, ctx.positions, ctx.seq_of_token, table,
+                         self.inv_freq, self.magnitude, q, cache.k_pages if cache.writable else None,
+                         cache.v_pages if cache.writable else None, h, g, d, v, self.position.rotary_dim, rt.page_size)
+        att = rt.empty(n, h * v)
+        if v == d:
+            self._attend(q, cache, att, ctx, table)
+        else:
+            ops.attention_generic(q, cache.k_pages, cache.v_pages, att, ctx.positions, ctx.seq_of_token, table,
+                                  h, g, d, rt.page_size, None, self.scale, value_dim=v)
+        # the product leaves in FP32 (or is added into the FP32 stream by the kernel itself): the residual sum
+        # sees it unrounded
+        return rt.linear(att, self.w_o, out_dtype=torch.float32, residual=residual)
+
+
 def _pairs_adjacent(w: torch.Tensor, n_heads: int, head_dim: int, rotary_dim: int) -> torch.Tensor:
     """Rows i and i + rot/2 of every head become rows 2i and 2i + 1; rows beyond rot stay."""
     out_dim, in_dim = w.shape
@@ -425,3 +542,4 @@ def _pairs_adjacent(w: torch.Tensor, n_heads: int, head_dim: int, rotary_dim: in
 register_part("mixer", "attention", PagedAttention, replace=True)
 register_part("mixer", "latent_attention", LatentAttention, replace=True)
 register_part("mixer", "conv_key_attention", ConvKeyAttention, replace=True)
+register_part("mixer", "normed_qk_attention", NormedQKAttention, replace=True)

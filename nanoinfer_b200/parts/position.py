@@ -45,8 +45,11 @@ class RotaryEncoding(Part):
     What a mixer reads from ANY position encoding: ``rotary_dim`` (0: nothing is rotated), ``inv_freq``,
     ``interleaved``, and ``head_slopes`` - None, or float32 [num_heads] on the device: the encoding adds
     slope[h] * (key position - query position) to the scaled attention scores of head h (then the mixer
-    uses the plain attention kernel, which takes such a bias, in either precision)."""
+    uses the plain attention kernel, which takes such a bias, in either precision); and ``magnitude``: a factor on
+    both the cosine and the sine (1 unless the encoding also scales what it rotates), which the kernels that take
+    it apply to the rotated dimensions only."""
     head_slopes = None
+    magnitude = 1.0
 
     def __init__(self, spec, hidden_size, weights, rt) -> None:
         super().__init__(spec, hidden_size, weights, rt)
@@ -74,9 +77,59 @@ class RotaryEncodingExact(RotaryEncoding):
         self.inv_freq = torch.from_numpy(np.power(float(spec.theta), -2.0 * i / spec.rotary_dim).astype(np.float32)).to(rt.device)
 
 
+class RotaryEncodingYarn(RotaryEncoding):
+    """Rotary encoding stretched for longer contexts by a ramp over the frequencies.  With f_i = theta^(-2i / n)
+    (n = rotary_dim) and the scaling's ``factor``, ``original`` (the context the frequencies were made for),
+    ``fast`` and ``slow`` (carried in the spec's RopeScaling as high_freq_factor and low_freq_factor):
+
+        c(t) = n ln(original / (2 pi t)) / (2 ln theta)        the dimension that turns t times over ``original``
+        lo = max(floor(c(fast)), 0),  hi = min(ceil(c(slow)), n - 1)
+        r_i = clamp((i - lo) / max(hi - lo, 0.001), 0, 1)
+        f_i <- f_i / factor * r_i + f_i * (1 - r_i)
+
+    so dimensions that turn often keep their frequency and slow ones are divided by ``factor``; cosine and sine
+    are both multiplied by ``magnitude`` = 0.1 ln(factor) + 1.  Without a scaling rule it is the plain encoding.
+    Frequencies are computed in double precision and rounded once; angles are FP32 products on the device."""
+
+    def __init__(self, spec, hidden_size, weights, rt) -> None:
+        Part.__init__(self, spec, hidden_size, weights, rt)
+        n = spec.rotary_dim
+        if n <= 0 or n % 2:
+            raise ConfigError(f"rotary_dim {n} must be positive and even")
+        if spec.pairing not in ("half", "interleaved"):
+            raise ConfigError(f"rope pairing '{spec.pairing}' must be 'half' or 'interleaved'")
+        self.rotary_dim = n
+        self.interleaved = spec.pairing == "interleaved"
+        freq, self.magnitude = yarn_frequencies(n, spec.theta, spec.scaling)
+        self.inv_freq = torch.from_numpy(freq.astype(np.float32)).to(rt.device)
+
+
+def yarn_frequencies(rotary_dim: int, theta: float, scaling):
+    """(float64 frequencies [rotary_dim / 2], magnitude) of RotaryEncodingYarn."""
+    i = np.arange(rotary_dim // 2, dtype=np.float64)
+    freq = np.power(float(theta), -2.0 * i / rotary_dim)
+    if scaling is None:
+        return freq, 1.0
+    if scaling.rope_type != "yarn":
+        raise ConfigError(f"rope scaling '{scaling.rope_type}' is not the ramp rule ('yarn')")
+    factor, original = float(scaling.factor), float(scaling.original_max_position_embeddings)
+    fast, slow = float(scaling.high_freq_factor), float(scaling.low_freq_factor)
+    if factor <= 0 or original <= 0 or fast <= 0 or slow <= 0 or theta <= 1.0:
+        raise ConfigError("rope scaling: factor, original, fast and slow must be positive (and the base above 1)")
+
+    def turns(t):
+        return rotary_dim * math.log(original / (2.0 * math.pi * t)) / (2.0 * math.log(theta))
+
+    lo = max(math.floor(turns(fast)), 0)
+    hi = min(math.ceil(turns(slow)), rotary_dim - 1)
+    ramp = np.clip((i - lo) / max(hi - lo, 0.001), 0.0, 1.0)
+    return freq / factor * ramp + freq * (1.0 - ramp), 0.1 * math.log(factor) + 1.0
+
+
 class NoEncoding(Part):
     """No position encoding: queries and keys are used as projected."""
     head_slopes = None
+    magnitude = 1.0
 
     def __init__(self, spec, hidden_size, weights, rt) -> None:
         super().__init__(spec, hidden_size, weights, rt)
@@ -87,4 +140,5 @@ class NoEncoding(Part):
 
 register_part("position", "rope", RotaryEncoding, replace=True)
 register_part("position", "rope_exact", RotaryEncodingExact, replace=True)
+register_part("position", "rope_yarn", RotaryEncodingYarn, replace=True)
 register_part("position", "none", NoEncoding, replace=True)

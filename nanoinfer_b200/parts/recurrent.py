@@ -100,4 +100,91 @@ class GatedDeltaRule(Part):
         return rt.linear(y, self.w_o, residual=residual)
 
 
+class LightningAttention(Part):
+    """Lightning attention: linear attention with a fixed decay per head.  Per head, with a matrix state S
+    [head_dim, value_dim] in FP32 that starts at zero and is carried from token to token for each request:
+
+        q = silu(W_q x), k = silu(W_k x)  (head_dim entries), v = silu(W_v x)  (value_dim entries)
+        S <- decay_head * S + k v^T;   o = S^T q                           (no other scale)
+
+    All heads' o side by side are divided by their root mean square (``norm_eps``), multiplied by a plain weight
+    and by sigmoid(W_g x), and leave through W_o.  ``decay`` (one number per head) and ``value_dim`` come in the
+    spec's extra.
+
+    The four projections of x are ONE product (rows q | k | v | gate); everything from there to the gated norm is
+    FP32 on the device (csrc/lightning.cu): a request's tokens of a step run in chunks whose inner products are
+    written out, so a prompt portion costs matrix products instead of a chain of rank-one updates, and a single
+    token is a chunk of one.  A step's kernels run exactly once, so the state advances by exactly the step's
+    tokens."""
+
+    kernel_modules = ("lightning",)       # libraries of csrc that this part's kernels live in
+
+    adds_into_residual = True
+    graph_safe = "all"
+
+    @staticmethod
+    def _dims(spec):
+        e = spec.extra_dict()
+        return spec.num_heads, spec.head_dim, int(e.get("value_dim", spec.head_dim))
+
+    @staticmethod
+    def weight_slots(spec, hidden_size: int) -> Dict[str, WeightSlot]:
+        h, d, v = LightningAttention._dims(spec)
+        return {"q": WeightSlot((h * d, hidden_size)), "k": WeightSlot((h * d, hidden_size)),
+                "v": WeightSlot((h * v, hidden_size)), "g": WeightSlot((h * v, hidden_size)),
+                "o": WeightSlot((hidden_size, h * v)), "norm": WeightSlot((h * v,), init="ones")}
+
+    def __init__(self, spec, hidden_size, weights, rt) -> None:
+        super().__init__(spec, hidden_size, weights, rt)
+        h, d, v = self._dims(spec)
+        decay = tuple(float(x) for x in spec.extra_dict().get("decay", ()))
+        if h <= 0 or v <= 0 or len(decay) != h:
+            raise ConfigError("lightning attention: heads and value size must be positive, with one decay per head")
+        if not 0 < d <= ops.LIGHTNING_MAX_DIM:
+            raise ConfigError(f"lightning attention: a key size of {d} is not supported (1 to {ops.LIGHTNING_MAX_DIM})")
+        self.H, self.D, self.V = h, d, v
+        self.eps = float(spec.extra_dict().get("norm_eps", 1e-6))
+        rows = [weights[s] for s in ("q", "k", "v", "g")]
+        self.gate_col = 2 * h * d + h * v
+        pad = -(self.gate_col + h * v) % 8         # zero rows, so that every row of the result starts on 16 bytes
+        if pad:
+            rows.append(torch.zeros(pad, hidden_size, dtype=weights["q"].dtype, device=weights["q"].device))
+        self.w_in = rt.weight(torch.cat(rows, dim=0))
+        self.w_o = rt.weight(weights["o"])
+        self.decay = torch.tensor(decay, dtype=torch.float32, device=rt.device)
+        self.norm_w = rt.gain(weights["norm"])
+
+    def cache_need(self):
+        return StateNeed((self.H * self.D * self.V,), "float32")
+
+    def weights_in_order(self) -> tuple:
+        return (self.w_in, self.w_o)
+
+    def can_fuse_norm(self, norm, n_rows: int) -> bool:
+        return self.rt.skinny(n_rows, self.hidden_size) and self.rt.fuses_norm(norm)
+
+    def forward(self, x: torch.Tensor, ctx, cache, residual=None):
+        return self.finish(self.rt.linear(x, self.w_in), ctx, cache, residual=residual)
+
+    def forward_fused_norm(self, h: torch.Tensor, norm, ctx, cache, residual=None):
+        """As forward, with x = norm(h): the norm runs inside the projection (steps of a few rows)."""
+        return self.finish(self.project(h, norm), ctx, cache, residual=residual)
+
+    def project(self, h: torch.Tensor, norm) -> torch.Tensor:
+        proj = self.rt.empty(h.shape[0], self.w_in.shape[0])
+        ops.gemv_norm_bf16(h, norm.gain, norm.eps, None, self.w_in, proj, ops.STORE_BF16)
+        return proj
+
+    def finish(self, proj: torch.Tensor, ctx, cache, residual=None):
+        rt = self.rt
+        n = proj.shape[0]
+        h, d, v = self.H, self.D, self.V
+        o = rt.empty(n, h * v, dtype=torch.float32)
+        ops.lightning_recurrence(proj, cache.state, ctx.cu_q, ctx.slots, ctx.n_seqs, self.decay, h, d, v, o)
+        y = rt.empty(n, h * v)
+        ops.lightning_gated_norm(o, proj, self.gate_col, self.norm_w, self.eps, y)
+        return rt.linear(y, self.w_o, out_dtype=torch.float32, residual=residual)
+
+
 register_part("mixer", "gated_delta", GatedDeltaRule, replace=True)
+register_part("mixer", "lightning", LightningAttention, replace=True)

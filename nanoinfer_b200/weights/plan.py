@@ -52,8 +52,11 @@ def tensor_plan(config: ModelConfig) -> List[PlannedTensor]:
         block = registry.part("arrangement", layer.arrangement)
         if hasattr(block, "weight_slots"):                    # weights of the arrangement itself
             add(("layer", i, "block"), block.weight_slots(layer, d))
-    if config.stream_inputs > 0:                              # vectors added to the stream before marked runs
-        add(("stream_inputs",), {"weight": WeightSlot((config.stream_inputs, d))})
+    if config.stream_inputs > 0:
+        if config.stream_input_kind == "project_with_embedding":      # x <- W [x; x0] before marked runs
+            add(("stream_inputs",), {"weight": WeightSlot((d, 2 * d))})
+        else:                                                  # vectors added to the stream before marked runs
+            add(("stream_inputs",), {"weight": WeightSlot((config.stream_inputs, d))})
     add(("final_norm",),
         registry.part("norm", config.final_norm.kind).weight_slots(config.final_norm, d))
     head = config.head_spec()
