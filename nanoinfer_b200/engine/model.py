@@ -58,6 +58,9 @@ class DecoderModel:
         # NormHandoff); the head keeps its own fused norm, so the last run hands nothing over
         firsts = [getattr(self.blocks[run.layer], "first_norm", lambda: None)() for run in config.schedule]
         self._norm_after = firsts[1:] + [None]
+        for r, run in enumerate(config.schedule[1:]):
+            if run.stream_input is not None:          # the stream changes between the two runs: nothing to prepare
+                self._norm_after[r] = None
         self._fused = False      # the fused decode step: not looked at yet / None (does not apply) / the object
 
     def cache_needs(self) -> List[Optional[object]]:

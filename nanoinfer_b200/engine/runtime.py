@@ -171,11 +171,13 @@ class Runtime:
         return y
 
     def experts_linear(self, a: torch.Tensor, w: torch.Tensor, offsets: torch.Tensor, tile_first: torch.Tensor,
-                       n_rows: int, token_of_row: Optional[torch.Tensor] = None, act: bool = False) -> torch.Tensor:
+                       n_rows: int, token_of_row: Optional[torch.Tensor] = None, act: bool = False,
+                       glu=ops.PLAIN_GLU, row_scale: Optional[torch.Tensor] = None) -> torch.Tensor:
         """One product per expert over rows laid out expert by expert: y[r] = a[r] . w[e]^T for the rows r of
         expert e's stretch [offsets[e], offsets[e + 1]) (int32 on the device; nothing is read on the host).
         ``token_of_row``: row r reads a[token_of_row[r]] instead.  ``act``: w is [E, 2N, K], gate rows then up
-        rows, and y = silu(gate) * up.  float32: the package's FFMA kernel, one ascending chain per element;
+        rows, and y = the gated unit's activation (``glu`` = (limit, slope, shift), ``row_scale`` float32 [rows]: see
+        ops.capped_glu; the default is silu(gate) * up).  float32: the package's FFMA kernel, one ascending chain per element;
         bfloat16 with sizes that are multiples of 8: a library grouped product (FP32 accumulation), as the
         other projections of prompt portions are library products; rows beyond the last stretch are undefined."""
         n_experts, wn, k = w.shape
@@ -187,10 +189,10 @@ class Runtime:
             if not act:
                 return y
             out = self.empty(n_rows, n)
-            ops.capped_glu(y, out, float("inf"), 1.0, 0.0)      # no cap, slope 1, no shift: silu(gate) * up, 16 bytes per thread
+            ops.capped_glu(y, out, *glu, row_scale=row_scale)      # 16 bytes per thread
             return out
         out = self.empty(n_rows, n)
-        ops.expert_gemm(a, token_of_row, w, out, offsets, tile_first, n_rows, act=act)
+        ops.expert_gemm(a, token_of_row, w, out, offsets, tile_first, n_rows, act=act, glu=glu, row_scale=row_scale)
         return out
 
     def skinny(self, n_rows: int, k: int) -> bool:

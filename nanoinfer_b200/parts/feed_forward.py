@@ -222,11 +222,20 @@ class SquaredReLU(Part):
 
 
 class RoutedExperts(Part):
-    """A routed feed-forward: ``experts`` small gated units W_down (silu(W_gate x) * (W_up x)) without biases, of
+    """A routed feed-forward: ``experts`` small gated units W_down act(W_gate x, W_up x) without biases, of
     which every token uses ``top``, plus ``identity_experts`` experts whose output is x itself (they have no
-    weights and are numbered after the real ones).  Router: s = softmax(W_router x) over all experts, FP32; the
-    chosen ones are those with the largest s + correction (``choice_bias``), their weights are s, divided by
-    their sum only if ``renormalize``; the output is the weighted sum, FP32.
+    weights and are numbered after the real ones).  Router: s = softmax(W_router x) over all experts, FP32 - or,
+    with ``scores`` = "sigmoid", s = sigmoid(W_router x), each expert on its own; the chosen ones are those with
+    the largest s + correction (``choice_bias``), their weights are s, divided by their sum only if
+    ``renormalize``; the output is the weighted sum, FP32.
+
+    The unit's activation is act(g, u) = g' sigmoid(slope g') (u' + shift) with g' = min(g, limit) and
+    u' = clamp(u, -limit, limit); ``limit`` (default: none), ``gate_slope`` (1) and ``up_shift`` (0) come in the
+    spec's extra, and their defaults make it silu(g) u.  With ``weight_on_input`` a chosen expert reads the token's
+    input MULTIPLIED by its weight and its output counts once: sum_e unit_e(s_e x).  Both first products are linear
+    in the input, so the weight multiplies their results, in FP32, before the limits - no scaled copy of the
+    input is made.  ``shared_ff`` > 0 adds one more unit of that size (limit ``shared_limit``, same slope and
+    shift) that every token runs on its plain input; its output is added.
 
     The experts' matrices are stacked ([E, 2F, d] gate rows then up rows, and [E, d, F]).  In bfloat16, steps of a
     few tokens with at least as many (token, choice) pairs as experts multiply with ALL experts' matrices (one
@@ -256,6 +265,11 @@ class RoutedExperts(Part):
             slots[f"e{j}.gate"] = WeightSlot((f, hidden_size))
             slots[f"e{j}.up"] = WeightSlot((f, hidden_size))
             slots[f"e{j}.down"] = WeightSlot((hidden_size, f))
+        sf = int(spec.extra_dict().get("shared_ff", 0))
+        if sf > 0:
+            slots["shared.gate"] = WeightSlot((sf, hidden_size))
+            slots["shared.up"] = WeightSlot((sf, hidden_size))
+            slots["shared.down"] = WeightSlot((hidden_size, sf))
         return slots
 
     def __init__(self, spec, hidden_size, weights, rt) -> None:
@@ -264,8 +278,19 @@ class RoutedExperts(Part):
         if n_real + n_id > ops.ROUTE_MAX_EXPERTS or not 0 < top <= n_real + n_id:
             raise ConfigError(f"routed experts: {n_real} + {n_id} experts (at most {ops.ROUTE_MAX_EXPERTS}) with top {top} "
                               f"is not supported")
+        e = spec.extra_dict()
         self.n_real, self.n_all, self.top, self.inter = n_real, n_real + n_id, top, f
-        self.renormalize = bool(spec.extra_dict().get("renormalize", False))
+        self.renormalize = bool(e.get("renormalize", False))
+        scores = e.get("scores", "softmax")
+        if scores not in ("softmax", "sigmoid"):
+            raise ConfigError(f"routed experts: scores '{scores}' is not known (softmax, sigmoid)")
+        self.sigmoid_scores = scores == "sigmoid"
+        self.weight_on_input = bool(e.get("weight_on_input", False))
+        slope, shift = float(e.get("gate_slope", 1.0)), float(e.get("up_shift", 0.0))
+        limit = e.get("limit")
+        self.glu = (float("inf") if limit is None else float(limit), slope, shift)
+        if not self.glu[0] > 0:
+            raise ConfigError("routed experts: the units' limit must be positive")
         self.w_router = rt.gain(weights["router"])                  # the router runs in FP32
         self.bias = rt.gain(weights["correction"]) if "correction" in weights else None
         if n_real > 0:
@@ -274,19 +299,44 @@ class RoutedExperts(Part):
             self.w_down = rt.weight(torch.stack([weights[f"e{j}.down"] for j in range(n_real)]))
         else:
             self.w_gate_up = self.w_down = None
+        self.shared_inter = int(e.get("shared_ff", 0))
+        self.w_shared_gate_up = self.w_shared_down = None
+        if self.shared_inter > 0:
+            sl = e.get("shared_limit")
+            self.shared_glu = (float("inf") if sl is None else float(sl), slope, shift)
+            if not self.shared_glu[0] > 0:
+                raise ConfigError("routed experts: the shared unit's limit must be positive")
+            self.w_shared_gate_up = rt.weight(torch.cat([weights["shared.gate"], weights["shared.up"]], dim=0))
+            self.w_shared_down = rt.weight(weights["shared.down"])
 
     def weights_in_order(self) -> tuple:
-        return (self.w_gate_up, self.w_down) if self.n_real > 0 else ()
+        routed = (self.w_gate_up, self.w_down) if self.n_real > 0 else ()
+        return routed + ((self.w_shared_gate_up, self.w_shared_down) if self.shared_inter > 0 else ())
 
     adds_normed = True          # forward accepts normed_into=(h, gain, eps): h += RMSNorm(output) * gain, returns None
 
-    def _combine(self, z, x, ids, weights, row_of_pair, n_real, normed_into, all_experts=0):
-        if normed_into is not None and x.shape[1] <= 12000:
-            h, gain, eps = normed_into
-            ops.route_combine_add_normed(z, x, ids, weights, row_of_pair, h, gain, eps, n_real, all_experts)
+    def _shared(self, x):
+        """The shared unit's output for every row, FP32 [T, d] (None without one)."""
+        if self.shared_inter <= 0:
             return None
-        y = self.rt.empty(x.shape[0], x.shape[1], dtype=torch.float32)
-        ops.route_combine(z, x, ids, weights, row_of_pair, y, n_real, all_experts)
+        rt = self.rt
+        gate_up = rt.linear(x, self.w_shared_gate_up)
+        act = rt.empty(x.shape[0], self.shared_inter)
+        ops.capped_glu(gate_up, act, *self.shared_glu)
+        return rt.linear(act, self.w_shared_down, out_dtype=torch.float32)
+
+    def _combine(self, z, x, ids, weights, row_of_pair, n_real, normed_into, all_experts=0):
+        unit = self.weight_on_input            # real experts' rows count once: their weight went into their input
+        y = self._shared(x)
+        if y is None and normed_into is not None and x.shape[1] <= 12000:
+            h, gain, eps = normed_into
+            ops.route_combine_add_normed(z, x, ids, weights, row_of_pair, h, gain, eps, n_real, all_experts, unit_real=unit)
+            return None
+        if y is None:
+            y = self.rt.empty(x.shape[0], x.shape[1], dtype=torch.float32)
+            ops.route_combine(z, x, ids, weights, row_of_pair, y, n_real, all_experts, unit_real=unit)
+        else:
+            ops.route_combine(z, x, ids, weights, row_of_pair, y, n_real, all_experts, unit_real=unit, accumulate=True)
         if normed_into is not None:
             ops.add_normed(normed_into[0], y, normed_into[1], normed_into[2])
             return None
@@ -305,7 +355,8 @@ class RoutedExperts(Part):
         rt = self.rt
         n = (x if x is not None else h).shape[0]
         dense = (rt.dtype == torch.bfloat16 and self.n_real > 0 and rt.skinny(n, self.hidden_size)
-                 and n * self.top >= self.n_real and self.inter % 8 == 0)
+                 and n * self.top >= self.n_real and self.inter % 8 == 0
+                 and not (self.weight_on_input and self.renormalize))     # that path scales by the plain scores
         if x is None:
             x = norm.forward(h, None)                 # the router and the identity experts read the normed rows
         gate_up_all = None
@@ -318,41 +369,52 @@ class RoutedExperts(Part):
                 ops.gemv_bf16(x, w_all, gate_up_all, ops.STORE_BF16)
         return x, gate_up_all
 
+    def _route(self, x, ids, weights, counts, all_scores=None):
+        ops.route(x, self.w_router, self.bias, ids, weights, counts, self.n_real, self.top, self.renormalize,
+                  sigmoid_scores=self.sigmoid_scores, all_scores=all_scores)
+
     def finish(self, first, ctx, normed_into=None):
         x, gate_up_all = first
         rt = self.rt
         n, d = x.shape
         top, n_real, f = self.top, self.n_real, self.inter
         pairs = n * top
-        i32 = torch.int32
+        i32, f32 = torch.int32, torch.float32
+        on_input = self.weight_on_input
         ids = rt.empty(n, top, dtype=i32)
-        weights = rt.empty(n, top, dtype=torch.float32)
+        weights = rt.empty(n, top, dtype=f32)
         if n_real == 0:
-            ops.route(x, self.w_router, self.bias, ids, weights, None, 0, top, self.renormalize)
+            self._route(x, ids, weights, None)
             return self._combine(x, x, ids, weights, None, 0, normed_into)
         if gate_up_all is not None:
             # every expert for every token: each matrix is read once, whoever chose it; the combination picks
-            ops.route(x, self.w_router, self.bias, ids, weights, None, n_real, top, self.renormalize)
+            scores = rt.empty(n, n_real, dtype=f32) if on_input else None
+            self._route(x, ids, weights, None, all_scores=scores)
             act = rt.empty(n * n_real, f)
-            ops.capped_glu(gate_up_all.view(n * n_real, 2 * f), act, float("inf"), 1.0, 0.0)     # silu(gate) * up
+            ops.capped_glu(gate_up_all.view(n * n_real, 2 * f), act, *self.glu,
+                           row_scale=scores.view(-1) if on_input else None)
             z = rt.heads_linear(act.view(n, n_real * f), self.w_down)                           # [T, E d]
             return self._combine(z.view(n * n_real, d), x, ids, weights, None, n_real, normed_into, all_experts=n_real)
         few = (rt.dtype == torch.bfloat16 and pairs <= ops.EXPERT_ROWS_MAX_PAIRS and d % 8 == 0 and f % 8 == 0)
         if few:
-            ops.route(x, self.w_router, self.bias, ids, weights, None, n_real, top, self.renormalize)
+            self._route(x, ids, weights, None)
             act = rt.empty(pairs, f)
-            ops.expert_rows(x, self.w_gate_up, act, ids, gather=True, act=True)
+            ops.expert_rows(x, self.w_gate_up, act, ids, gather=True, act=True, glu=self.glu,
+                            row_scale=weights.view(-1) if on_input else None)
             z = rt.empty(pairs, d)
             ops.expert_rows(act, self.w_down, z, ids, gather=False, act=False)
             return self._combine(z, x, ids, weights, None, n_real, normed_into)
         counts = rt.workspace("routed_counts", ops.ROUTE_MAX_EXPERTS, i32, zero=True)
-        ops.route(x, self.w_router, self.bias, ids, weights, counts, n_real, top, self.renormalize)
+        self._route(x, ids, weights, counts)
         meta = torch.zeros(3 * (n_real + 1) + 2 * pairs, dtype=i32, device=rt.device)     # rows nobody owns name token 0
         offsets, tile_first, cursor = (meta[i * (n_real + 1):(i + 1) * (n_real + 1)] for i in range(3))
         row_of_pair = meta[3 * (n_real + 1):3 * (n_real + 1) + pairs]
         token_of_row = meta[3 * (n_real + 1) + pairs:]
-        ops.route_layout(ids, counts, offsets, tile_first, cursor, row_of_pair, token_of_row, n_real)
-        act = rt.experts_linear(x, self.w_gate_up, offsets, tile_first, pairs, token_of_row=token_of_row, act=True)
+        weight_of_row = torch.zeros(pairs, dtype=f32, device=rt.device) if on_input else None
+        ops.route_layout(ids, counts, offsets, tile_first, cursor, row_of_pair, token_of_row, n_real,
+                         weights=weights if on_input else None, weight_of_row=weight_of_row)
+        act = rt.experts_linear(x, self.w_gate_up, offsets, tile_first, pairs, token_of_row=token_of_row, act=True,
+                                glu=self.glu, row_scale=weight_of_row)
         z = rt.experts_linear(act, self.w_down, offsets, tile_first, pairs)
         return self._combine(z, x, ids, weights, row_of_pair, n_real, normed_into)
 
