@@ -2,7 +2,7 @@
 """Decode and prefill throughput of the engine at the Llama 3.2 1B shape with random weights.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch 8] [--layers 16] [--impl ours|reference]
-    python bench.py --design runevik|vuvalorn [--sizes w1024,w2048]     (another design beside the Llama model of equal size)
+    python bench.py --design runevik|vuvalorn|tazulix [--sizes w1024,w2048]     (another design beside the Llama model of equal size)
 
 A "step" is one decode step of the whole batch.  Every request starts at a context of 2,048
 tokens and decodes W + K tokens (by default to 4,096).  Prints ONE JSON line:
@@ -414,7 +414,33 @@ def vuvalorn_config(z):
             "loop": {"start": 2, "stop": 4, "times": 2}, "layers": [layer(i) for i in range(z["layers"] - 2)]}
 
 
-DESIGN_CONFIGS = {"runevik": runevik_config, "vuvalorn": vuvalorn_config}
+def tazulix_config(z):
+    """As many layer runs as the Llama model has layers: two layers fewer, a span of two that runs twice.  Every
+    third layer is a lightning layer (as many heads of 128 x 128 as the attention layers have), the others
+    attention with normed projections and half of each head rotated with ramp-scaled frequencies.  Layers alternate
+    between the squared unit (1.5 times the dense width: two matrices instead of three) and 16 routed units of a
+    quarter of the dense width with 3 chosen plus a shared one, so a token multiplies with as many feed-forward
+    weights either way."""
+    heads = z["width"] // 128
+
+    def layer(i):
+        if i % 3 == 2:
+            decay = [1.0 - 2.0 ** -(2 + 8 * h / max(heads - 1, 1)) for h in range(heads)]
+            kind, mixer = "lightning", {"heads": heads, "dim": 128, "vdim": 128, "decay": decay}
+        else:
+            kind, mixer = "attention", {"heads": heads, "kv_heads": z["kv_heads"], "dim": 128, "vdim": 128, "scale": 128 ** -0.5,
+                                        "rot": {"dims": 64, "base": 500000.0,
+                                                "scaling": {"factor": 8.0, "original": 8192, "fast": 32.0, "slow": 1.0}}}
+        mlp = {"kind": "dense", "ff": z["ff"] * 3 // 2} if i % 2 == 0 else \
+            {"kind": "moe", "expert": {"ff": z["ff"] // 4, "limit": 7.0}, "router": {"experts": 16, "top": 3},
+             "shared": {"ff": z["ff"] // 4, "limit": 7.0}}
+        return {"type": kind, "mixer": mixer, "mlp": mlp}
+    return {"architecture": "Tazulix", "vocab": z["vocab"], "width": z["width"], "norm": {"eps": 1e-6},
+            "embedding": {"scale": float(z["width"]) ** 0.5},
+            "loop": {"start": 2, "stop": 4, "times": 2}, "layers": [layer(i) for i in range(z["layers"] - 2)]}
+
+
+DESIGN_CONFIGS = {"runevik": runevik_config, "vuvalorn": vuvalorn_config, "tazulix": tazulix_config}
 
 
 def llama_config(z):

@@ -6,93 +6,194 @@
 //
 // Everything after the projections is FP32 whatever the tensors' type.
 //
-// lightning_chunk_kernel runs a request's tokens of this step in chunks of LT_C tokens.  With n tokens in a chunk,
-// S0 the state before it and p[i] = decay^i (a table built by repeated multiplication, as the recurrence itself
-// would):
+// A request's tokens of a step run in chunks of LT_C tokens.  With n tokens in a chunk, S0 the state before it and
+// p[i] = decay^i (a table built by repeated multiplication, as the recurrence itself would):
 //
 //   A[t, j] = (q_t . k_j) p[t - j]                      for j <= t            (scores; no softmax)
 //   o_t     = sum_(j <= t) A[t, j] v_j  +  p[t + 1] S0^T q_t
 //   S       = p[n] S0 + sum_j p[n - 1 - j] k_j v_j^T
 //
-// which is the recurrence written out; only the order of the additions differs.  A single token is a chunk of
-// one.  One block owns (request, head, LT_VT value columns): its tile of S stays in shared memory from the first
-// chunk to the last and is read and written once per step.  All three products are register-tiled FP32 FMA
-// loops over shared memory (the design keeps the scores and the state in 32 bits, so no tensor cores).
+// which is the recurrence written out; only the order of the additions differs.  Chunks depend on one another only
+// through S, so a step is three launches:
+//
+//   lightning_chunk_kv_kernel    every chunk's own sum_j p[n - 1 - j] k_j v_j^T, all chunks at once, into a buffer
+//   lightning_scan_kernel        per request and head, chunk after chunk: the buffer's entry becomes the state BEFORE
+//                                the chunk, the running state takes the chunk's sum; the last one is the new state
+//   lightning_chunk_out_kernel   every chunk's read-out from its scores, its values and the state before it, all chunks
+//                                at once
+//
+// and a step of single tokens is one launch (lightning_token_kernel) that reads and writes every state once.
+// All products are register-tiled FP32 FMA loops over shared memory (the design keeps the scores and the state in
+// 32 bits, so no tensor cores).
 #include "common.cuh"
 
 #define LT_C 64          // tokens per chunk
-#define LT_VT 16         // value columns per block
 #define LT_THREADS 256
+#define LT_KV_TILE 64    // rows and columns of a chunk's sum that one block of lightning_chunk_kv_kernel owns
 
 __device__ __forceinline__ float lt_silu(float z) { return z / (1.0f + expf(-z)); }
 
+// The first chunk of request `seq` in the buffer: the chunks of the requests before it, counted by all threads.
+__device__ __forceinline__ int lt_chunk_base(const int* __restrict__ cu_q, int seq, int* scratch) {
+    if (threadIdx.x == 0) *scratch = 0;
+    __syncthreads();
+    int mine = 0;
+    for (int s = threadIdx.x; s < seq; s += blockDim.x) mine += (cu_q[s + 1] - cu_q[s] + LT_C - 1) / LT_C;
+    if (mine) atomicAdd(scratch, mine);
+    __syncthreads();
+    return *scratch;
+}
+
+// grid (chunks of the longest request x row tiles x column tiles, H, requests); buf [chunks, H, D, V]
 template <typename T>
 __global__ void __launch_bounds__(LT_THREADS)
-lightning_chunk_kernel(const T* __restrict__ proj, int ld, float* __restrict__ state, long long state_stride,
-                       const int* __restrict__ cu_q, const int* __restrict__ slots, const float* __restrict__ decay,
-                       float* __restrict__ out, int H, int D, int V) {
-    extern __shared__ __align__(16) float sm[];
-    const int DP = (D + 3) & ~3;             // rows padded to whole float4s (zeros)
-    const int QS = DP + 4;                   // row stride of Qs / Ks: neighbouring rows start 4 banks apart
-    float* Ss = sm;                          // [DP][LT_VT]
-    float* Qs = Ss + DP * LT_VT;             // [LT_C][QS]
-    float* Ks = Qs + LT_C * QS;              // [LT_C][QS]
-    float* Vs = Ks + LT_C * QS;              // [LT_C][LT_VT]
-    float* As = Vs + LT_C * LT_VT;           // [LT_C][LT_C + 4]
-    float* pw = As + LT_C * (LT_C + 4);      // [LT_C + 1]
-    constexpr int AS = LT_C + 4;
-
-    const int tid = threadIdx.x;
-    const int v0 = blockIdx.x * LT_VT, head = blockIdx.y, seq = blockIdx.z;
-    const int vt = min(LT_VT, V - v0);
+lightning_chunk_kv_kernel(const T* __restrict__ proj, int ld, const int* __restrict__ cu_q, const float* __restrict__ decay,
+                          float* __restrict__ buf, int H, int D, int V, int d_tiles, int v_tiles) {
+    __shared__ __align__(16) float Ks[LT_C][LT_KV_TILE];
+    __shared__ __align__(16) float Vs[LT_C][LT_KV_TILE];
+    __shared__ float pw[LT_C + 1];
+    __shared__ int base_s;
+    const int tid = threadIdx.x, head = blockIdx.y, seq = blockIdx.z;
+    const int chunk = blockIdx.x / (d_tiles * v_tiles), tile = blockIdx.x % (d_tiles * v_tiles);
+    const int d0 = (tile / v_tiles) * LT_KV_TILE, v0 = (tile % v_tiles) * LT_KV_TILE;
     const int t0 = cu_q[seq], t1 = cu_q[seq + 1];
-    if (t1 <= t0) return;
-    float* S = state + (size_t)slots[seq] * state_stride + (size_t)head * D * V + v0;
-    const float dec = decay[head];
+    const int c0 = t0 + chunk * LT_C;
+    if (c0 >= t1) return;
+    const int base = lt_chunk_base(cu_q, seq, &base_s);
+    const int n = min(LT_C, t1 - c0);
     if (tid == 0) {
+        const float dec = decay[head];
         float p = 1.0f;
         for (int i = 0; i <= LT_C; ++i) { pw[i] = p; p *= dec; }
     }
-    for (int i = tid; i < DP * LT_VT; i += LT_THREADS) {
-        const int d = i / LT_VT, v = i % LT_VT;
-        Ss[i] = (d < D && v < vt) ? S[(size_t)d * V + v] : 0.f;
+    __syncthreads();
+    const T* xk = proj + (size_t)(H + head) * D + d0;
+    const T* xv = proj + (size_t)2 * H * D + (size_t)head * V + v0;
+    for (int i = tid; i < n * LT_KV_TILE; i += LT_THREADS) {
+        const int t = i / LT_KV_TILE, c = i % LT_KV_TILE;
+        const size_t row = (size_t)(c0 + t) * ld;
+        Ks[t][c] = d0 + c < D ? lt_silu(ni_to_float(xk[row + c])) : 0.f;
+        Vs[t][c] = v0 + c < V ? lt_silu(ni_to_float(xv[row + c])) * pw[n - 1 - t] : 0.f;      // decayed to the chunk's end
     }
-    // the triangular tile of the score phase that this thread owns (4 x 4 scores; tiles on or below the diagonal)
-    int a_ti = -1, a_ji = 0;
-    if (tid < (LT_C / 4) * (LT_C / 4 + 1) / 2) {
-        int ti = 0, rest = tid;
-        while (rest > ti) { rest -= ti + 1; ++ti; }
-        a_ti = ti;
-        a_ji = rest;
+    __syncthreads();
+    const int vg = (tid % 16) * 4, dg = (tid / 16) * 4;
+    float acc[4][4];
+#pragma unroll
+    for (int a = 0; a < 4; ++a)
+#pragma unroll
+        for (int b = 0; b < 4; ++b) acc[a][b] = 0.f;
+    for (int j = 0; j < n; ++j) {
+        const float4 k4 = *reinterpret_cast<const float4*>(&Ks[j][dg]);
+        const float4 v4 = *reinterpret_cast<const float4*>(&Vs[j][vg]);
+        const float kk[4] = {k4.x, k4.y, k4.z, k4.w}, vv[4] = {v4.x, v4.y, v4.z, v4.w};
+#pragma unroll
+        for (int a = 0; a < 4; ++a)
+#pragma unroll
+            for (int b = 0; b < 4; ++b) acc[a][b] = fmaf(kk[a], vv[b], acc[a][b]);
+    }
+    float* out = buf + ((size_t)(base + chunk) * H + head) * D * V;
+#pragma unroll
+    for (int a = 0; a < 4; ++a)
+#pragma unroll
+        for (int b = 0; b < 4; ++b)
+            if (d0 + dg + a < D && v0 + vg + b < V) out[(size_t)(d0 + dg + a) * V + v0 + vg + b] = acc[a][b];
+}
+
+// grid (ceil(D V / threads), H, requests)
+__global__ void lightning_scan_kernel(float* __restrict__ state, long long state_stride, const int* __restrict__ cu_q,
+                                      const int* __restrict__ slots, const float* __restrict__ decay,
+                                      float* __restrict__ buf, int H, int D, int V) {
+    __shared__ int base_s;
+    const int head = blockIdx.y, seq = blockIdx.z;
+    const int len = cu_q[seq + 1] - cu_q[seq];
+    if (len <= 0) return;
+    const int base = lt_chunk_base(cu_q, seq, &base_s);
+    const int e = blockIdx.x * blockDim.x + threadIdx.x;
+    if (e >= D * V) return;
+    const float dec = decay[head];
+    float p_full = 1.0f;
+    for (int i = 0; i < LT_C; ++i) p_full *= dec;
+    float* S = state + (size_t)slots[seq] * state_stride + (size_t)head * D * V + e;
+    float s = *S;
+    const size_t stride = (size_t)H * D * V;
+    float* b = buf + ((size_t)base * H + head) * D * V + e;
+    for (int done = 0; done < len; done += LT_C, b += stride) {
+        const int n = min(LT_C, len - done);
+        float pn = p_full;
+        if (n < LT_C) {
+            pn = 1.0f;
+            for (int i = 0; i < n; ++i) pn *= dec;
+        }
+        const float own = *b;
+        *b = s;                                   // what the chunk's read-out starts from
+        s = fmaf(pn, s, own);
+    }
+    *S = s;
+}
+
+// grid (chunks of the longest request x column tiles of VT, H, requests); buf holds the state before every chunk
+template <typename T, int VT>
+__global__ void __launch_bounds__(LT_THREADS)
+lightning_chunk_out_kernel(const T* __restrict__ proj, int ld, const int* __restrict__ cu_q, const float* __restrict__ decay,
+                           const float* __restrict__ buf, float* __restrict__ out, int H, int D, int V, int v_tiles) {
+    extern __shared__ __align__(16) float sm[];
+    __shared__ int base_s;
+    constexpr int TT = LT_C * VT / (LT_THREADS * 4);        // tokens per thread of the read-out (4 columns each)
+    constexpr int AS = LT_C + 4;
+    const int DP = (D + 3) & ~3;             // rows padded to whole float4s (zeros)
+    const int QS = DP + 4;                   // row stride of Qs / Ks: neighbouring rows start 4 banks apart
+    float* Ss = sm;                          // [DP][VT]
+    float* Qs = Ss + DP * VT;                // [LT_C][QS]
+    float* Ks = Qs + LT_C * QS;              // [LT_C][QS]
+    float* Vs = Ks + LT_C * QS;              // [LT_C][VT]
+    float* As = Vs + LT_C * VT;              // [LT_C][AS]
+    float* pw = As + LT_C * AS;              // [LT_C + 1]
+
+    const int tid = threadIdx.x, head = blockIdx.y, seq = blockIdx.z;
+    const int chunk = blockIdx.x / v_tiles, v0 = (blockIdx.x % v_tiles) * VT;
+    const int t0 = cu_q[seq], t1 = cu_q[seq + 1];
+    const int c0 = t0 + chunk * LT_C;
+    if (c0 >= t1) return;
+    const int base = lt_chunk_base(cu_q, seq, &base_s);
+    const int n = min(LT_C, t1 - c0), n4 = (n + 3) & ~3;
+    const int vt = min(VT, V - v0);
+    if (tid == 0) {
+        const float dec = decay[head];
+        float p = 1.0f;
+        for (int i = 0; i <= LT_C; ++i) { pw[i] = p; p *= dec; }
+    }
+    const float* S0 = buf + ((size_t)(base + chunk) * H + head) * D * V + v0;
+    for (int i = tid; i < DP * VT; i += LT_THREADS) {
+        const int d = i / VT, v = i % VT;
+        Ss[i] = (d < D && v < vt) ? S0[(size_t)d * V + v] : 0.f;
     }
     const T* xq = proj + (size_t)head * D;
     const T* xk = proj + (size_t)(H + head) * D;
     const T* xv = proj + (size_t)2 * H * D + (size_t)head * V + v0;
-
-    for (int c0 = t0; c0 < t1; c0 += LT_C) {
-        const int n = min(LT_C, t1 - c0), n4 = (n + 3) & ~3;
-        __syncthreads();                     // the chunk before is done with Qs, Ks, Vs, As (and pw, Ss are written)
-        for (int i = tid; i < n4 * DP; i += LT_THREADS) {
-            const int t = i / DP, d = i - t * DP;
-            const bool in = t < n && d < D;
-            const size_t at = (size_t)(c0 + t) * ld + d;
-            Qs[t * QS + d] = in ? lt_silu(ni_to_float(xq[at])) : 0.f;
-            Ks[t * QS + d] = in ? lt_silu(ni_to_float(xk[at])) : 0.f;
-        }
-        for (int i = tid; i < n4 * LT_VT; i += LT_THREADS) {
-            const int t = i / LT_VT, v = i % LT_VT;
-            Vs[i] = (t < n && v < vt) ? lt_silu(ni_to_float(xv[(size_t)(c0 + t) * ld + v])) : 0.f;
-        }
-        __syncthreads();
-        // ---- scores: A[t, j] = (q_t . k_j) p[t - j], zero above the diagonal
-        if (a_ti >= 0 && a_ti * 4 < n4) {
+    for (int i = tid; i < n4 * DP; i += LT_THREADS) {
+        const int t = i / DP, d = i - t * DP;
+        const bool in = t < n && d < D;
+        const size_t at = (size_t)(c0 + t) * ld + d;
+        Qs[t * QS + d] = in ? lt_silu(ni_to_float(xq[at])) : 0.f;
+        Ks[t * QS + d] = in ? lt_silu(ni_to_float(xk[at])) : 0.f;
+    }
+    for (int i = tid; i < n4 * VT; i += LT_THREADS) {
+        const int t = i / VT, v = i % VT;
+        Vs[i] = (t < n && v < vt) ? lt_silu(ni_to_float(xv[(size_t)(c0 + t) * ld + v])) : 0.f;
+    }
+    __syncthreads();
+    // ---- scores: A[t, j] = (q_t . k_j) p[t - j], zero above the diagonal; a thread owns one 4 x 4 tile on or below it
+    if (tid < (LT_C / 4) * (LT_C / 4 + 1) / 2) {
+        int ti = 0, ji = tid;
+        while (ji > ti) { ji -= ti + 1; ++ti; }
+        if (ti * 4 < n4) {
             float acc[4][4];
 #pragma unroll
             for (int a = 0; a < 4; ++a)
 #pragma unroll
                 for (int b = 0; b < 4; ++b) acc[a][b] = 0.f;
-            const float* qp = Qs + a_ti * 4 * QS;
-            const float* kp = Ks + a_ji * 4 * QS;
+            const float* qp = Qs + ti * 4 * QS;
+            const float* kp = Ks + ji * 4 * QS;
             for (int d = 0; d < DP; d += 4) {
                 float4 qv[4], kv[4];
 #pragma unroll
@@ -114,81 +215,128 @@ lightning_chunk_kernel(const T* __restrict__ proj, int ld, float* __restrict__ s
             for (int a = 0; a < 4; ++a)
 #pragma unroll
                 for (int b = 0; b < 4; ++b) {
-                    const int t = a_ti * 4 + a, j = a_ji * 4 + b;
+                    const int t = ti * 4 + a, j = ji * 4 + b;
                     As[t * AS + j] = j <= t ? acc[a][b] * pw[t - j] : 0.f;
                 }
         }
-        __syncthreads();
-        // ---- read-out: o_t = sum_(j <= t) A[t, j] v_j + p[t + 1] S0^T q_t; thread = 4 tokens x 1 value column
-        {
-            const int v = tid % LT_VT, tg = tid / LT_VT;         // 16 groups of 4 tokens
-            if (tg * 4 < n4) {
-                float intra[4] = {0.f, 0.f, 0.f, 0.f}, inter[4] = {0.f, 0.f, 0.f, 0.f};
-                const int j_end = tg * 4 + 4;                     // scores beyond the diagonal are zero
-                for (int j = 0; j < j_end; j += 4) {
-                    float4 av[4];
+    }
+    __syncthreads();
+    // ---- read-out: o_t = sum_(j <= t) A[t, j] v_j + p[t + 1] S0^T q_t; a thread owns TT tokens x 4 value columns
+    const int vg = (tid % (VT / 4)) * 4, tg = (tid / (VT / 4)) * TT;
+    if (tg >= n4) return;
+    float intra[TT][4], inter[TT][4];
 #pragma unroll
-                    for (int a = 0; a < 4; ++a) av[a] = *reinterpret_cast<const float4*>(As + (tg * 4 + a) * AS + j);
-                    const float w0 = Vs[j * LT_VT + v], w1 = Vs[(j + 1) * LT_VT + v], w2 = Vs[(j + 2) * LT_VT + v],
-                                w3 = Vs[(j + 3) * LT_VT + v];
+    for (int a = 0; a < TT; ++a)
 #pragma unroll
-                    for (int a = 0; a < 4; ++a) {
-                        intra[a] = fmaf(av[a].x, w0, intra[a]);
-                        intra[a] = fmaf(av[a].y, w1, intra[a]);
-                        intra[a] = fmaf(av[a].z, w2, intra[a]);
-                        intra[a] = fmaf(av[a].w, w3, intra[a]);
-                    }
-                }
-                for (int d = 0; d < DP; d += 4) {
-                    float4 qv[4];
+        for (int b = 0; b < 4; ++b) intra[a][b] = inter[a][b] = 0.f;
+    const int j_end = (tg + TT + 3) & ~3;                     // scores beyond the diagonal are zero
+    for (int j = 0; j < j_end; j += 4) {
+        float4 av[TT], wv[4];
 #pragma unroll
-                    for (int a = 0; a < 4; ++a) qv[a] = *reinterpret_cast<const float4*>(Qs + (tg * 4 + a) * QS + d);
-                    const float s0 = Ss[d * LT_VT + v], s1 = Ss[(d + 1) * LT_VT + v], s2 = Ss[(d + 2) * LT_VT + v],
-                                s3 = Ss[(d + 3) * LT_VT + v];
+        for (int a = 0; a < TT; ++a) av[a] = *reinterpret_cast<const float4*>(As + (tg + a) * AS + j);
 #pragma unroll
-                    for (int a = 0; a < 4; ++a) {
-                        inter[a] = fmaf(qv[a].x, s0, inter[a]);
-                        inter[a] = fmaf(qv[a].y, s1, inter[a]);
-                        inter[a] = fmaf(qv[a].z, s2, inter[a]);
-                        inter[a] = fmaf(qv[a].w, s3, inter[a]);
-                    }
-                }
-                if (v < vt) {
+        for (int jj = 0; jj < 4; ++jj) wv[jj] = *reinterpret_cast<const float4*>(Vs + (j + jj) * VT + vg);
 #pragma unroll
-                    for (int a = 0; a < 4; ++a) {
-                        const int t = tg * 4 + a;
-                        if (t < n) out[(size_t)(c0 + t) * H * V + (size_t)head * V + v0 + v] = fmaf(pw[t + 1], inter[a], intra[a]);
-                    }
-                }
-            }
-        }
-        __syncthreads();
-        // ---- the values take their decay to the chunk's end: v_j <- p[n - 1 - j] v_j
-        for (int i = tid; i < n * LT_VT; i += LT_THREADS) Vs[i] *= pw[n - 1 - i / LT_VT];
-        __syncthreads();
-        // ---- state: S = p[n] S0 + sum_j k_j (p[n - 1 - j] v_j)^T; thread = 1 value column x every 16th row group of 4
-        {
-            const int v = tid % LT_VT;
-            const float pn = pw[n];
-            for (int d = (tid / LT_VT) * 4; d < DP; d += (LT_THREADS / LT_VT) * 4) {
-                float acc[4] = {0.f, 0.f, 0.f, 0.f};
-                for (int j = 0; j < n; ++j) {
-                    const float4 kv = *reinterpret_cast<const float4*>(Ks + j * QS + d);
-                    const float w = Vs[j * LT_VT + v];
-                    acc[0] = fmaf(kv.x, w, acc[0]);
-                    acc[1] = fmaf(kv.y, w, acc[1]);
-                    acc[2] = fmaf(kv.z, w, acc[2]);
-                    acc[3] = fmaf(kv.w, w, acc[3]);
-                }
+        for (int a = 0; a < TT; ++a) {
+            const float aa[4] = {av[a].x, av[a].y, av[a].z, av[a].w};
 #pragma unroll
-                for (int a = 0; a < 4; ++a) Ss[(d + a) * LT_VT + v] = fmaf(pn, Ss[(d + a) * LT_VT + v], acc[a]);
+            for (int jj = 0; jj < 4; ++jj) {
+                intra[a][0] = fmaf(aa[jj], wv[jj].x, intra[a][0]);
+                intra[a][1] = fmaf(aa[jj], wv[jj].y, intra[a][1]);
+                intra[a][2] = fmaf(aa[jj], wv[jj].z, intra[a][2]);
+                intra[a][3] = fmaf(aa[jj], wv[jj].w, intra[a][3]);
             }
         }
     }
+    for (int d = 0; d < DP; d += 4) {
+        float4 qv[TT], sv[4];
+#pragma unroll
+        for (int a = 0; a < TT; ++a) qv[a] = *reinterpret_cast<const float4*>(Qs + (tg + a) * QS + d);
+#pragma unroll
+        for (int dd = 0; dd < 4; ++dd) sv[dd] = *reinterpret_cast<const float4*>(Ss + (d + dd) * VT + vg);
+#pragma unroll
+        for (int a = 0; a < TT; ++a) {
+            const float qq[4] = {qv[a].x, qv[a].y, qv[a].z, qv[a].w};
+#pragma unroll
+            for (int dd = 0; dd < 4; ++dd) {
+                inter[a][0] = fmaf(qq[dd], sv[dd].x, inter[a][0]);
+                inter[a][1] = fmaf(qq[dd], sv[dd].y, inter[a][1]);
+                inter[a][2] = fmaf(qq[dd], sv[dd].z, inter[a][2]);
+                inter[a][3] = fmaf(qq[dd], sv[dd].w, inter[a][3]);
+            }
+        }
+    }
+#pragma unroll
+    for (int a = 0; a < TT; ++a) {
+        const int t = tg + a;
+        if (t >= n) continue;
+        float* o = out + (size_t)(c0 + t) * H * V + (size_t)head * V + v0 + vg;
+#pragma unroll
+        for (int b = 0; b < 4; ++b)
+            if (vg + b < vt) o[b] = fmaf(pw[t + 1], inter[a][b], intra[a][b]);
+    }
+}
+
+// A step of single tokens: S <- decay S + k v^T, o = S^T q; every state is read and written once.
+// grid (column tiles of 128, H, requests); a warp owns every 8th row, a lane 4 neighbouring columns.
+template <typename T>
+__global__ void __launch_bounds__(LT_THREADS)
+lightning_token_kernel(const T* __restrict__ proj, int ld, float* __restrict__ state, long long state_stride,
+                       const int* __restrict__ cu_q, const int* __restrict__ slots, const float* __restrict__ decay,
+                       float* __restrict__ out, int H, int D, int V) {
+    extern __shared__ __align__(16) float sm[];
+    float* qs = sm;                          // [D]
+    float* ks = qs + D;                      // [D]
+    float* part = ks + D;                    // [8 warps][128 columns]
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int v0 = blockIdx.x * 128, head = blockIdx.y, seq = blockIdx.z;
+    const int t = cu_q[seq];
+    if (cu_q[seq + 1] <= t) return;
+    const T* row = proj + (size_t)t * ld;
+    for (int d = tid; d < D; d += LT_THREADS) {
+        qs[d] = lt_silu(ni_to_float(row[(size_t)head * D + d]));
+        ks[d] = lt_silu(ni_to_float(row[(size_t)(H + head) * D + d]));
+    }
+    const int vc = v0 + lane * 4;
+    float vv[4], acc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int b = 0; b < 4; ++b) vv[b] = vc + b < V ? lt_silu(ni_to_float(row[(size_t)2 * H * D + (size_t)head * V + vc + b])) : 0.f;
     __syncthreads();
-    for (int i = tid; i < D * LT_VT; i += LT_THREADS) {
-        const int d = i / LT_VT, v = i % LT_VT;
-        if (v < vt) S[(size_t)d * V + v] = Ss[i];
+    const float dec = decay[head];
+    float* S = state + (size_t)slots[seq] * state_stride + (size_t)head * D * V;
+    const bool wide = (V % 4 == 0) && ((reinterpret_cast<size_t>(S) & 15) == 0) && vc + 3 < V;
+    for (int d = warp; d < D; d += LT_THREADS / 32) {
+        float* sp = S + (size_t)d * V + vc;
+        const float k = ks[d], q = qs[d];
+        if (wide) {
+            float4 s4 = *reinterpret_cast<float4*>(sp);
+            s4.x = fmaf(dec, s4.x, k * vv[0]);
+            s4.y = fmaf(dec, s4.y, k * vv[1]);
+            s4.z = fmaf(dec, s4.z, k * vv[2]);
+            s4.w = fmaf(dec, s4.w, k * vv[3]);
+            *reinterpret_cast<float4*>(sp) = s4;
+            acc[0] = fmaf(s4.x, q, acc[0]);
+            acc[1] = fmaf(s4.y, q, acc[1]);
+            acc[2] = fmaf(s4.z, q, acc[2]);
+            acc[3] = fmaf(s4.w, q, acc[3]);
+        } else {
+#pragma unroll
+            for (int b = 0; b < 4; ++b)
+                if (vc + b < V) {
+                    const float s1 = fmaf(dec, sp[b], k * vv[b]);
+                    sp[b] = s1;
+                    acc[b] = fmaf(s1, q, acc[b]);
+                }
+        }
+    }
+#pragma unroll
+    for (int b = 0; b < 4; ++b) part[warp * 128 + lane * 4 + b] = acc[b];
+    __syncthreads();
+    if (tid < 128 && v0 + tid < V) {
+        float o = 0.f;
+#pragma unroll
+        for (int w = 0; w < LT_THREADS / 32; ++w) o += part[w * 128 + tid];
+        out[(size_t)t * H * V + (size_t)head * V + v0 + tid] = o;
     }
 }
 
@@ -211,31 +359,67 @@ __global__ void lightning_gated_norm_kernel(const float* __restrict__ o, const T
     }
 }
 
-static size_t lt_smem_bytes(int D) {
+static size_t lt_out_smem_bytes(int D, int VT) {
     const int DP = (D + 3) & ~3;
-    return ((size_t)DP * LT_VT + 2 * (size_t)LT_C * (DP + 4) + (size_t)LT_C * LT_VT + (size_t)LT_C * (LT_C + 4) + LT_C + 1) *
-           sizeof(float);
+    return ((size_t)DP * VT + 2 * (size_t)LT_C * (DP + 4) + (size_t)LT_C * VT + (size_t)LT_C * (LT_C + 4) + LT_C + 1) * sizeof(float);
+}
+
+// The most chunks that requests of n_tokens tokens in all can have.
+NI_EXPORT int ni_lightning_max_chunks(int n_tokens, int n_seqs) {
+    const long long whole = (long long)n_tokens / LT_C + n_seqs;
+    return whole < n_tokens ? (int)whole : n_tokens;
 }
 
 // proj [T, ld] with columns q (H D) | k (H D) | v (H V) | ...; state FP32 [slots, state_stride] holding S [H, D, V] of
-// every request; decay FP32 [H]; out FP32 [T, H V].  The state advances by the step's tokens.
+// every request; decay FP32 [H]; out FP32 [T, H V].  The state advances by the step's tokens.  max_q_len: the most
+// tokens that one request brings (1: a step of single tokens, which needs no buffer); buf FP32 with room for
+// buf_chunks x H D V, at least ni_lightning_max_chunks(n_tokens, n_seqs) chunks.
 NI_EXPORT int ni_lightning_recurrence(const void* proj, int dtype, int ld, float* state, long long state_stride,
                                       const int* cu_q, const int* slots, const float* decay, float* out, int n_tokens,
-                                      int n_seqs, int H, int D, int V, cudaStream_t stream) {
+                                      int n_seqs, int max_q_len, float* buf, long long buf_chunks, int H, int D, int V,
+                                      cudaStream_t stream) {
     if (n_tokens <= 0 || n_seqs <= 0) return NI_OK;
-    if (H <= 0 || D <= 0 || V <= 0 || ld < 2 * H * D + H * V || state_stride < (long long)H * D * V) return NI_ERR_BAD_ARGUMENT;
-    const size_t smem = lt_smem_bytes(D);
-    if (smem > 200 * 1024 || H > 65535 || n_seqs > 65535) return NI_ERR_UNSUPPORTED_SIZE;
-    dim3 grid((V + LT_VT - 1) / LT_VT, H, n_seqs);
+    if (H <= 0 || D <= 0 || V <= 0 || ld < 2 * H * D + H * V || state_stride < (long long)H * D * V || max_q_len <= 0)
+        return NI_ERR_BAD_ARGUMENT;
+    if (dtype != NI_DTYPE_F32 && dtype != NI_DTYPE_BF16) return NI_ERR_BAD_ARGUMENT;
+    if (H > 65535 || n_seqs > 65535) return NI_ERR_UNSUPPORTED_SIZE;
+    if (max_q_len == 1) {
+        dim3 grid((V + 127) / 128, H, n_seqs);
+        const size_t smem = ((size_t)2 * D + (LT_THREADS / 32) * 128) * sizeof(float);
+        if (smem > 48 * 1024) return NI_ERR_UNSUPPORTED_SIZE;
+        if (dtype == NI_DTYPE_F32)
+            lightning_token_kernel<float><<<grid, LT_THREADS, smem, stream>>>((const float*)proj, ld, state, state_stride, cu_q,
+                                                                               slots, decay, out, H, D, V);
+        else
+            lightning_token_kernel<__nv_bfloat16><<<grid, LT_THREADS, smem, stream>>>((const __nv_bfloat16*)proj, ld, state,
+                                                                                       state_stride, cu_q, slots, decay, out, H, D, V);
+        NI_RETURN_LAUNCH_STATUS();
+    }
+    if (buf == nullptr || buf_chunks < ni_lightning_max_chunks(n_tokens, n_seqs)) return NI_ERR_BAD_ARGUMENT;
+    const int VT = D <= 128 ? 64 : 32;
+    const size_t smem = lt_out_smem_bytes(D, VT);
+    if (smem > 227 * 1024) return NI_ERR_UNSUPPORTED_SIZE;
+    const int per_seq = (max_q_len + LT_C - 1) / LT_C;
+    const int d_tiles = (D + LT_KV_TILE - 1) / LT_KV_TILE, kv_tiles = (V + LT_KV_TILE - 1) / LT_KV_TILE, v_tiles = (V + VT - 1) / VT;
+    dim3 grid_kv(per_seq * d_tiles * kv_tiles, H, n_seqs), grid_scan((D * V + LT_THREADS - 1) / LT_THREADS, H, n_seqs),
+        grid_out(per_seq * v_tiles, H, n_seqs);
 #define LAUNCH(T)                                                                                                        \
     do {                                                                                                                 \
-        cudaFuncSetAttribute(lightning_chunk_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);        \
-        lightning_chunk_kernel<T><<<grid, LT_THREADS, smem, stream>>>((const T*)proj, ld, state, state_stride, cu_q,    \
-                                                                      slots, decay, out, H, D, V);                       \
+        lightning_chunk_kv_kernel<T><<<grid_kv, LT_THREADS, 0, stream>>>((const T*)proj, ld, cu_q, decay, buf, H, D, V,  \
+                                                                         d_tiles, kv_tiles);                             \
+        lightning_scan_kernel<<<grid_scan, LT_THREADS, 0, stream>>>(state, state_stride, cu_q, slots, decay, buf, H, D, V); \
+        if (VT == 64) {                                                                                                  \
+            cudaFuncSetAttribute(lightning_chunk_out_kernel<T, 64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+            lightning_chunk_out_kernel<T, 64><<<grid_out, LT_THREADS, smem, stream>>>((const T*)proj, ld, cu_q, decay, buf, \
+                                                                                      out, H, D, V, v_tiles);            \
+        } else {                                                                                                         \
+            cudaFuncSetAttribute(lightning_chunk_out_kernel<T, 32>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+            lightning_chunk_out_kernel<T, 32><<<grid_out, LT_THREADS, smem, stream>>>((const T*)proj, ld, cu_q, decay, buf, \
+                                                                                      out, H, D, V, v_tiles);            \
+        }                                                                                                                \
     } while (0)
     if (dtype == NI_DTYPE_F32) LAUNCH(float);
-    else if (dtype == NI_DTYPE_BF16) LAUNCH(__nv_bfloat16);
-    else return NI_ERR_BAD_ARGUMENT;
+    else LAUNCH(__nv_bfloat16);
 #undef LAUNCH
     NI_RETURN_LAUNCH_STATUS();
 }

@@ -10,6 +10,9 @@
     python -m nanoinfer_b200.kernels.microbench attention_prefill --tokens 2048 --q-heads 16 --head-dim 128 --score-cap 30
     python -m nanoinfer_b200.kernels.microbench conv_attention --batch 1 --tokens 2048 --heads 16 --kv-heads 8 --dim 128
     python -m nanoinfer_b200.kernels.microbench routed --tokens 2048 --width 2048 --ff 2048 --experts 16 --identity 2 --top 4
+    python -m nanoinfer_b200.kernels.microbench lightning --batch 1 --tokens 2048 --heads 16 --dim 128 --vdim 128
+    python -m nanoinfer_b200.kernels.microbench qk_norm_rope --batch 1 --tokens 2048 --heads 16 --kv-heads 8 --dim 128
+    python -m nanoinfer_b200.kernels.microbench routed --tokens 8 --experts 16 --identity 0 --top 3 --sigmoid --on-input --shared-ff 2048
 
 Each case runs its kernel over several distinct copies of its inputs in turn (together
 larger than the L2 cache, so every run reads from HBM), times it with CUDA events after
@@ -430,6 +433,61 @@ def conv_attention(args) -> None:
           f"normed addition (width {width}) {us_add:.2f} us ({n * width * 12 / us_add / 1e3:.0f} GB/s)")
 
 
+def lightning(args) -> None:
+    """Lightning attention's kernels at --batch requests of --tokens tokens each: the recurrence (chunked over a
+    request's tokens) and the gated norm.  States of several request sets are used in turn, so that single-token
+    steps read theirs from HBM."""
+    b, t, H, D, V = args.batch, args.tokens, args.heads, args.dim, args.vdim
+    n = b * t
+    cols = 2 * H * D + 2 * H * V
+    bf = torch.bfloat16
+    copies = max(2, min(32, -(-2 * L2_BYTES // (b * H * D * V * 4)))) if t == 1 else 2
+    g = torch.Generator(device=DEV).manual_seed(0)
+    states = [torch.randn(b, H * D * V, device=DEV, generator=g) * 0.1 for _ in range(copies)]
+    proj = (torch.randn(n, cols, device=DEV, generator=g) * 0.5).to(bf)
+    decay = torch.full((H,), 0.99, device=DEV)
+    norm_w = torch.ones(H * V, device=DEV)
+    cu = torch.arange(0, n + 1, t, dtype=torch.int32, device=DEV)
+    slots = torch.arange(b, dtype=torch.int32, device=DEV)
+    o = torch.empty(n, H * V, device=DEV)
+    y = torch.empty(n, H * V, dtype=bf, device=DEV)
+    buf = torch.empty(ops.lightning_max_chunks(n, b) * H * D * V, device=DEV) if t > 1 else None
+    us_rec = _time([lambda st=st: ops.lightning_recurrence(proj, st, cu, slots, b, decay, H, D, V, o, max_q_len=t, buf=buf) for st in states], args.iters)
+    us_norm = _time([lambda: ops.lightning_gated_norm(o, proj, 2 * H * D + H * V, norm_w, 1e-6, y)], args.iters)
+    state_bytes = 2 * b * H * D * V * 4                      # S read and written once per step
+    flops = 4.0 * n * H * D * V                              # one multiply-add per state entry for the update, one for the read-out
+    print(f"lightning batch={b} tokens={t} heads={H} dim={D} vdim={V}: recurrence {us_rec:.2f} us "
+          f"({state_bytes / us_rec / 1e3:.0f} GB/s of state, {flops / us_rec / 1e6:.2f} TFLOP/s FP32 of the recurrence's own work), "
+          f"gated norm {us_norm:.2f} us ({n * H * V * (4 + 2 + 2) / us_norm / 1e3:.0f} GB/s)")
+
+
+def qk_norm_rope(args) -> None:
+    """What stands between the projection and the attention of a mixer with normed projections, at --batch requests of
+    --tokens tokens each: bias + the two whole-projection norms + rotation + cache write, one launch."""
+    b, t, H, G, D = args.batch, args.tokens, args.heads, args.kv_heads, args.dim
+    n, page = b * t, 16
+    cols = (H + 2 * G) * D
+    bf = torch.bfloat16
+    g = torch.Generator(device=DEV).manual_seed(0)
+    copies = max(2, min(32, -(-2 * L2_BYTES // (n * cols * 4))))
+    projs = [torch.randn(n, cols, device=DEV, generator=g).to(bf) for _ in range(copies)]
+    bias = torch.randn(cols, device=DEV, generator=g) * 0.1
+    qg, kg = torch.ones(H * D, device=DEV), torch.ones(G * D, device=DEV)
+    start = args.context
+    per_seq = -(-(start + t) // page)
+    k_pages = torch.zeros(b * per_seq, G, page, D, dtype=bf, device=DEV)
+    v_pages = torch.zeros_like(k_pages)
+    table = torch.randperm(b * per_seq, device=DEV, generator=g).int().view(b, per_seq)
+    pos = (torch.arange(t, device=DEV).repeat(b) + start).int()
+    seq = torch.repeat_interleave(torch.arange(b, device=DEV), t).int()
+    inv_freq = torch.pow(500000.0, -2.0 * torch.arange(D // 4, device=DEV) / (D // 2)).float()
+    q = torch.empty(n, H * D, dtype=bf, device=DEV)
+    us = _time([lambda p=p: ops.qk_norm_rope(p, bias, qg, kg, 1e-6, pos, seq, table, inv_freq, 1.2, q, k_pages, v_pages, H, G, D, D,
+                                             D // 2, page) for p in projs], args.iters)
+    moved = n * cols * 2 * 2                              # every column read once and written once
+    print(f"qk_norm_rope batch={b} tokens={t} heads={H}/{G} dim={D}: {us:.2f} us ({moved / us / 1e3:.0f} GB/s)")
+
+
 def routed(args) -> None:
     """The routed feed-forward at --tokens rows: the router, then the whole part (all its launches, its output normed
     and added into an FP32 stream as a sandwich layer asks for it), in bfloat16."""
@@ -441,28 +499,43 @@ def routed(args) -> None:
     g = torch.Generator(device=DEV).manual_seed(0)
     rt = Runtime(device=torch.device(DEV), dtype=bf, page_size=16)
     ops.preload(["routed", "pointwise", "gemv_bf16", "gemv_ksplit"])
-    spec = FeedForwardSpec(kind="routed_experts", intermediate_size=f,
-                           extra=(("experts", E), ("identity_experts", I), ("top", top), ("choice_bias", True)))
+    extra = [("experts", E), ("identity_experts", I), ("top", top), ("choice_bias", not args.sigmoid)]
+    if args.sigmoid:
+        extra += [("scores", "sigmoid")]
+    if args.on_input:
+        extra += [("weight_on_input", True), ("limit", 7.0), ("gate_slope", 1.702), ("up_shift", 1.0)]
+    if args.shared_ff:
+        extra += [("shared_ff", args.shared_ff), ("shared_limit", 7.0)]
+    spec = FeedForwardSpec(kind="routed_experts", intermediate_size=f, extra=tuple(extra))
 
     def weights():
-        w = {"router": torch.randn(E + I, d, device=DEV, generator=g).to(bf) * (0.02 if args.flat_router else 0.5),
-             "correction": torch.randn(E + I, device=DEV, generator=g).to(bf) * 0.01}
+        w = {"router": torch.randn(E + I, d, device=DEV, generator=g).to(bf) * (0.02 if args.flat_router else 0.5)}
+        if not args.sigmoid:
+            w["correction"] = torch.randn(E + I, device=DEV, generator=g).to(bf) * 0.01
+        if args.shared_ff:
+            for k, shape in (("gate", (args.shared_ff, d)), ("up", (args.shared_ff, d)), ("down", (d, args.shared_ff))):
+                w[f"shared.{k}"] = (torch.randn(shape, device=DEV, generator=g) * 0.02).to(bf)
         for e in range(E):
             for k, shape in (("gate", (f, d)), ("up", (f, d)), ("down", (d, f))):
                 w[f"e{e}.{k}"] = (torch.randn(shape, device=DEV, generator=g) * 0.02).to(bf)
         return w
-    expert_bytes = E * 3 * f * d * 2
+    expert_bytes = (E * f + args.shared_ff) * 3 * d * 2
     parts = [RoutedExperts(spec, d, weights(), rt) for _ in range(max(2, min(8, -(-2 * L2_BYTES // expert_bytes))))]
     x = torch.randn(n, d, device=DEV, generator=g).to(bf)
     ids = torch.empty(n, top, dtype=torch.int32, device=DEV)
     wts = torch.empty(n, top, dtype=torch.float32, device=DEV)
-    us_route = _time([lambda p=p: ops.route(x, p.w_router, p.bias, ids, wts, None, E, top) for p in parts], args.iters)
+    us_route = _time([lambda p=p: ops.route(x, p.w_router, p.bias, ids, wts, None, E, top, sigmoid_scores=args.sigmoid)
+                      for p in parts], args.iters)
     h, gain = torch.zeros(n, d, device=DEV), torch.ones(d, device=DEV)
+    if args.plain_add:        # a pre-norm layer: the part's output is added into the stream as it is
+        run = lambda p: ops.residual_add(h, p.forward(x, None))
+    else:                     # a sandwich layer: normed, then added
+        run = lambda p: p.forward(x, None, normed_into=(h, gain, 1e-6))
     for p in parts:
-        p.forward(x, None, normed_into=(h, gain, 1e-6))                       # sizes the workspaces outside the captured loop
-    us_all = _time([lambda p=p: p.forward(x, None, normed_into=(h, gain, 1e-6)) for p in parts], args.iters)
+        run(p)                                                                # sizes the workspaces outside the captured loop
+    us_all = _time([lambda p=p: run(p) for p in parts], args.iters)
     chosen = torch.unique(ids[ids < E]).numel()
-    flops = 2.0 * (ids < E).sum().item() * 3 * f * d
+    flops = 2.0 * ((ids < E).sum().item() * f + n * args.shared_ff) * 3 * d
     print(f"routed tokens={n} width={d} expert ff={f} experts={E}+{I} top={top}: router {us_route:.2f} us; whole part "
           f"{us_all:.2f} us ({chosen} of {E} experts chosen; {expert_bytes / us_all / 1e3:.0f} GB/s if every expert is read "
           f"once, {flops / us_all / 1e6:.1f} TFLOP/s of chosen products)")
@@ -571,6 +644,21 @@ def main() -> None:
     p.add_argument("--taps", type=int, default=4)
     p.add_argument("--width", type=int, default=2048)
     p.set_defaults(fn=conv_attention)
+    p = sub.add_parser("lightning")
+    p.add_argument("--batch", type=int, default=8)
+    p.add_argument("--tokens", type=int, default=1)
+    p.add_argument("--heads", type=int, default=16)
+    p.add_argument("--dim", type=int, default=128)
+    p.add_argument("--vdim", type=int, default=128)
+    p.set_defaults(fn=lightning)
+    p = sub.add_parser("qk_norm_rope")
+    p.add_argument("--batch", type=int, default=1)
+    p.add_argument("--tokens", type=int, default=2048)
+    p.add_argument("--context", type=int, default=0, help="tokens each request holds already")
+    p.add_argument("--heads", type=int, default=16)
+    p.add_argument("--kv-heads", type=int, default=8)
+    p.add_argument("--dim", type=int, default=128)
+    p.set_defaults(fn=qk_norm_rope)
     p = sub.add_parser("routed")
     p.add_argument("--tokens", type=int, default=2048)
     p.add_argument("--width", type=int, default=2048)
@@ -578,6 +666,10 @@ def main() -> None:
     p.add_argument("--experts", type=int, default=16)
     p.add_argument("--identity", type=int, default=2)
     p.add_argument("--top", type=int, default=4)
+    p.add_argument("--sigmoid", action="store_true", help="scores are a sigmoid per expert (no choice bias)")
+    p.add_argument("--on-input", action="store_true", help="the weight multiplies the expert's input; capped units")
+    p.add_argument("--shared-ff", type=int, default=0, help="width of a shared unit that every token runs (0: none)")
+    p.add_argument("--plain-add", action="store_true", help="the output is added into the stream without a norm")
     p.add_argument("--flat-router", action="store_true", help="router weights so small that the choice bias decides (all tokens choose alike)")
     p.set_defaults(fn=routed)
     for sp in sub.choices.values():

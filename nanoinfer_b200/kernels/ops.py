@@ -57,7 +57,8 @@ _SIGNATURES = {
         "ni_qk_norm_rope": [_P, _I, _I, _P, _P, _P, _F, _P, _P, _P, _I, _P, _F, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P],
     },
     "lightning": {
-        "ni_lightning_recurrence": [_P, _I, _I, _P, _LL, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P],
+        "ni_lightning_recurrence": [_P, _I, _I, _P, _LL, _P, _P, _P, _P, _I, _I, _I, _P, _LL, _I, _I, _I, _P],
+        "ni_lightning_max_chunks": [_I, _I],
         "ni_lightning_gated_norm": [_P, _P, _I, _I, _I, _P, _F, _P, _I, _I, _P],
     },
     "conv_attention": {
@@ -599,19 +600,37 @@ def qk_norm_rope(qkv, bias, q_gain, k_gain, eps, positions, seq_of_token, block_
 LIGHTNING_MAX_DIM = 256      # the largest key size whose chunk buffers fit a block's shared memory
 
 
-def lightning_recurrence(proj, state, cu_q, slots, n_seqs, decay, n_heads, dim, vdim, out) -> None:
+def lightning_max_chunks(n_tokens: int, n_seqs: int) -> int:
+    """The most chunks that ``n_seqs`` requests with ``n_tokens`` tokens in all are cut into (the size of
+    lightning_recurrence's buffer, in units of H dim vdim floats)."""
+    return int(load("lightning").ni_lightning_max_chunks(int(n_tokens), int(n_seqs)))
+
+
+def lightning_recurrence(proj, state, cu_q, slots, n_seqs, decay, n_heads, dim, vdim, out, max_q_len=None, buf=None) -> None:
     """Linear attention with a decay per head over a step's tokens, request by request: with q, k [H, dim] and v
     [H, vdim] = silu of proj's columns (q | k | v | ...), S <- decay_h S + k v^T and out = S^T q, all float32;
     ``state`` float32 [slots, >= H dim vdim] holds every request's S and advances by the step's tokens; out float32
-    [T, H vdim]."""
+    [T, H vdim].  ``max_q_len``: the most tokens one request brings (None: as many as there are tokens); a step
+    of single tokens is one launch, others run in chunks and need ``buf`` (float32, lightning_max_chunks(T, n_seqs)
+    x H dim vdim entries; None: allocated here)."""
     n = proj.shape[0]
     if proj.shape[1] < n_heads * (2 * dim + vdim) or out.shape != (n, n_heads * vdim) or decay.numel() != n_heads \
             or state.shape[1] < n_heads * dim * vdim:
         raise KernelError("lightning_recurrence: shapes do not agree")
+    max_q_len = n if max_q_len is None else int(max_q_len)
+    per_chunk = n_heads * dim * vdim
+    chunks = 0
+    if max_q_len > 1:
+        chunks = lightning_max_chunks(n, n_seqs)
+        if buf is None:
+            buf = torch.empty(chunks * per_chunk, dtype=torch.float32, device=proj.device)
+        elif buf.numel() < chunks * per_chunk:
+            raise KernelError("lightning_recurrence: the chunk buffer is too small")
     _check(load("lightning").ni_lightning_recurrence(
         _dev(proj, "proj"), _code(proj, "proj"), proj.shape[1], _dev(state, "state", torch.float32), state.shape[1],
         _dev(cu_q, "cu_q", torch.int32), _dev(slots, "slots", torch.int32), _dev(decay, "decay", torch.float32),
-        _dev(out, "out", torch.float32), n, n_seqs, n_heads, dim, vdim, _stream()), "lightning_recurrence")
+        _dev(out, "out", torch.float32), n, n_seqs, max_q_len, _dev(buf, "buf", torch.float32) if chunks else None,
+        chunks, n_heads, dim, vdim, _stream()), "lightning_recurrence")
 
 
 def lightning_gated_norm(o, proj, col0, weight, eps, y) -> None:

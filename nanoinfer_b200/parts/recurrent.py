@@ -113,9 +113,10 @@ class LightningAttention(Part):
 
     The four projections of x are ONE product (rows q | k | v | gate); everything from there to the gated norm is
     FP32 on the device (csrc/lightning.cu): a request's tokens of a step run in chunks whose inner products are
-    written out, so a prompt portion costs matrix products instead of a chain of rank-one updates, and a single
-    token is a chunk of one.  A step's kernels run exactly once, so the state advances by exactly the step's
-    tokens."""
+    written out, so a prompt portion costs matrix products instead of a chain of rank-one updates - every chunk's own
+    sum at once, a scan over the chunks that leaves the state before each, every chunk's read-out at once -, and a
+    step of single tokens is one launch that reads and writes every state once.  A step's kernels run exactly
+    once, so the state advances by exactly the step's tokens."""
 
     kernel_modules = ("lightning",)       # libraries of csrc that this part's kernels live in
 
@@ -180,7 +181,11 @@ class LightningAttention(Part):
         n = proj.shape[0]
         h, d, v = self.H, self.D, self.V
         o = rt.empty(n, h * v, dtype=torch.float32)
-        ops.lightning_recurrence(proj, cache.state, ctx.cu_q, ctx.slots, ctx.n_seqs, self.decay, h, d, v, o)
+        buf = None
+        if ctx.max_q_len > 1:       # chunks: every chunk's own sum, then the state before it (one buffer for all layers)
+            buf = rt.workspace("lightning_chunks", ops.lightning_max_chunks(n, ctx.n_seqs) * h * d * v, torch.float32)
+        ops.lightning_recurrence(proj, cache.state, ctx.cu_q, ctx.slots, ctx.n_seqs, self.decay, h, d, v, o,
+                                 max_q_len=ctx.max_q_len, buf=buf)
         y = rt.empty(n, h * v)
         ops.lightning_gated_norm(o, proj, self.gate_col, self.norm_w, self.eps, y)
         return rt.linear(y, self.w_o, out_dtype=torch.float32, residual=residual)

@@ -246,7 +246,7 @@ def test_attention_with_values_of_another_size(dtype, Hq, Hkv, D, V):
     assert (out[1].float() - out[2].float()).abs().max() > 0.2
 
 
-@pytest.mark.parametrize("H, D, V", [(3, 20, 12), (2, 64, 64), (1, 32, 16), (5, 9, 7), (2, 8, 24), (1, 130, 20), (2, 128, 128)])
+@pytest.mark.parametrize("H, D, V", [(3, 20, 12), (2, 64, 64), (1, 32, 16), (5, 9, 7), (2, 8, 24), (1, 130, 20), (2, 128, 128), (1, 256, 40), (2, 16, 200)])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_lightning_recurrence_alone(dtype, H, D, V):
     """Four requests in one launch - 70 tokens (more than a chunk) from an empty state, one token and 64 tokens from
@@ -284,6 +284,21 @@ def test_lightning_recurrence_alone(dtype, H, D, V):
     scale = max(1.0, want_o.abs().max().item())
     torch.testing.assert_close(out.double().cpu() / scale, want_o / scale, **tol)
     assert torch.equal(state_d[3].cpu(), state[3])                # nobody's slot
+    # then one more token for each of three of them, as a step of single tokens (one launch, no chunks)
+    step = (torch.randn(3, cols + 2, generator=g) * 0.8).to(dtype)
+    before = state_d.cpu()
+    out1 = torch.empty(3, H * V, dtype=torch.float32, device=DEV)
+    ops.lightning_recurrence(step.to(DEV), state_d, torch.tensor([0, 1, 2, 3], dtype=torch.int32, device=DEV),
+                             torch.tensor([4, 2, 0], dtype=torch.int32, device=DEV), 3, decay.to(DEV), H, D, V, out1, max_q_len=1)
+    for r, slot in enumerate([4, 2, 0]):
+        x = step[r].double()
+        S, o1 = lightning_token(before[slot, :H * D * V].double().view(H, D, V), silu(x[:H * D]).view(H, D),
+                                silu(x[H * D:2 * H * D]).view(H, D), silu(x[2 * H * D:2 * H * D + H * V]).view(H, V), decay.double())
+        scale = max(1.0, S.abs().max().item(), o1.abs().max().item())
+        torch.testing.assert_close(state_d[slot, :H * D * V].double().cpu().view(H, D, V) / scale, S / scale, **tol)
+        torch.testing.assert_close(out1[r].double().cpu() / scale, o1.reshape(-1) / scale, **tol)
+        assert torch.equal(state_d[slot, H * D * V:].cpu(), state[slot, H * D * V:])
+    assert torch.equal(state_d[3].cpu(), state[3]) and torch.equal(state_d[1].cpu(), before[1])
     w = 1 + 0.3 * torch.randn(H * V, generator=g)
     y = torch.empty(n, H * V, dtype=dtype, device=DEV)
     gate_col = 2 * H * D + H * V
