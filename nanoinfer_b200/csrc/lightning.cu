@@ -33,6 +33,52 @@
 
 __device__ __forceinline__ float lt_silu(float z) { return z / (1.0f + expf(-z)); }
 
+// dst[r * dst_stride + c] = f(src[r * ld + c]) * scale[r] for r < rows, c < cols (zero for rows .. rows_pad - 1 and
+// c in cols .. cols_pad - 1).  16 bytes per load when every row starts on 16 bytes and cols is a multiple of the
+// vector's elements.
+template <typename T, bool SILU>
+__device__ __forceinline__ void lt_load_tile(const T* __restrict__ src, size_t ld, int rows, int rows_pad, int cols, int cols_pad,
+                                             float* __restrict__ dst, int dst_stride, const float* __restrict__ row_scale,
+                                             int scale_last) {
+    constexpr int VEC = 16 / sizeof(T);
+    const bool wide = cols % VEC == 0 && ld % VEC == 0 && (reinterpret_cast<size_t>(src) & 15) == 0 && cols_pad % 4 == 0 &&
+                      dst_stride % 4 == 0;
+    if (wide) {
+        const int per_row = cols_pad / VEC + (cols_pad % VEC ? 1 : 0);
+        for (int i = threadIdx.x; i < rows_pad * per_row; i += LT_THREADS) {
+            const int r = i / per_row, c = (i - r * per_row) * VEC;
+            float v[VEC];
+            if (r < rows && c < cols) {
+                const uint4 raw = *reinterpret_cast<const uint4*>(src + (size_t)r * ld + c);
+                const T* e = reinterpret_cast<const T*>(&raw);
+                const float sc = row_scale ? row_scale[scale_last - r] : 1.0f;
+#pragma unroll
+                for (int k = 0; k < VEC; ++k) {
+                    const float z = ni_to_float(e[k]);
+                    v[k] = (SILU ? lt_silu(z) : z) * sc;
+                }
+            } else {
+#pragma unroll
+                for (int k = 0; k < VEC; ++k) v[k] = 0.f;
+            }
+#pragma unroll
+            for (int k = 0; k < VEC; k += 4)
+                if (c + k < cols_pad)
+                    *reinterpret_cast<float4*>(dst + r * dst_stride + c + k) = make_float4(v[k], v[k + 1], v[k + 2], v[k + 3]);
+        }
+        return;
+    }
+    for (int i = threadIdx.x; i < rows_pad * cols_pad; i += LT_THREADS) {
+        const int r = i / cols_pad, c = i - r * cols_pad;
+        float v = 0.f;
+        if (r < rows && c < cols) {
+            const float z = ni_to_float(src[(size_t)r * ld + c]);
+            v = (SILU ? lt_silu(z) : z) * (row_scale ? row_scale[scale_last - r] : 1.0f);
+        }
+        dst[r * dst_stride + c] = v;
+    }
+}
+
 // The first chunk of request `seq` in the buffer: the chunks of the requests before it, counted by all threads.
 __device__ __forceinline__ int lt_chunk_base(const int* __restrict__ cu_q, int seq, int* scratch) {
     if (threadIdx.x == 0) *scratch = 0;
@@ -69,12 +115,8 @@ lightning_chunk_kv_kernel(const T* __restrict__ proj, int ld, const int* __restr
     __syncthreads();
     const T* xk = proj + (size_t)(H + head) * D + d0;
     const T* xv = proj + (size_t)2 * H * D + (size_t)head * V + v0;
-    for (int i = tid; i < n * LT_KV_TILE; i += LT_THREADS) {
-        const int t = i / LT_KV_TILE, c = i % LT_KV_TILE;
-        const size_t row = (size_t)(c0 + t) * ld;
-        Ks[t][c] = d0 + c < D ? lt_silu(ni_to_float(xk[row + c])) : 0.f;
-        Vs[t][c] = v0 + c < V ? lt_silu(ni_to_float(xv[row + c])) * pw[n - 1 - t] : 0.f;      // decayed to the chunk's end
-    }
+    lt_load_tile<T, true>(xk + (size_t)c0 * ld, ld, n, n, min(LT_KV_TILE, D - d0), LT_KV_TILE, &Ks[0][0], LT_KV_TILE, nullptr, 0);
+    lt_load_tile<T, true>(xv + (size_t)c0 * ld, ld, n, n, min(LT_KV_TILE, V - v0), LT_KV_TILE, &Vs[0][0], LT_KV_TILE, pw, n - 1);   // decayed to the chunk's end
     __syncthreads();
     const int vg = (tid % 16) * 4, dg = (tid / 16) * 4;
     float acc[4][4];
@@ -117,16 +159,23 @@ __global__ void lightning_scan_kernel(float* __restrict__ state, long long state
     float s = *S;
     const size_t stride = (size_t)H * D * V;
     float* b = buf + ((size_t)base * H + head) * D * V + e;
-    for (int done = 0; done < len; done += LT_C, b += stride) {
-        const int n = min(LT_C, len - done);
-        float pn = p_full;
-        if (n < LT_C) {
-            pn = 1.0f;
-            for (int i = 0; i < n; ++i) pn *= dec;
+    const int chunks = (len + LT_C - 1) / LT_C;
+    for (int c = 0; c < chunks; c += 8) {
+        float own[8];                             // loaded together: the chain below waits for memory once per group
+#pragma unroll
+        for (int i = 0; i < 8; ++i) own[i] = c + i < chunks ? b[(size_t)(c + i) * stride] : 0.f;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            if (c + i >= chunks) break;
+            const int n = min(LT_C, len - (c + i) * LT_C);
+            float pn = p_full;
+            if (n < LT_C) {
+                pn = 1.0f;
+                for (int k = 0; k < n; ++k) pn *= dec;
+            }
+            b[(size_t)(c + i) * stride] = s;       // what the chunk's read-out starts from
+            s = fmaf(pn, s, own[i]);
         }
-        const float own = *b;
-        *b = s;                                   // what the chunk's read-out starts from
-        s = fmaf(pn, s, own);
     }
     *S = s;
 }
@@ -163,24 +212,10 @@ lightning_chunk_out_kernel(const T* __restrict__ proj, int ld, const int* __rest
         for (int i = 0; i <= LT_C; ++i) { pw[i] = p; p *= dec; }
     }
     const float* S0 = buf + ((size_t)(base + chunk) * H + head) * D * V + v0;
-    for (int i = tid; i < DP * VT; i += LT_THREADS) {
-        const int d = i / VT, v = i % VT;
-        Ss[i] = (d < D && v < vt) ? S0[(size_t)d * V + v] : 0.f;
-    }
-    const T* xq = proj + (size_t)head * D;
-    const T* xk = proj + (size_t)(H + head) * D;
-    const T* xv = proj + (size_t)2 * H * D + (size_t)head * V + v0;
-    for (int i = tid; i < n4 * DP; i += LT_THREADS) {
-        const int t = i / DP, d = i - t * DP;
-        const bool in = t < n && d < D;
-        const size_t at = (size_t)(c0 + t) * ld + d;
-        Qs[t * QS + d] = in ? lt_silu(ni_to_float(xq[at])) : 0.f;
-        Ks[t * QS + d] = in ? lt_silu(ni_to_float(xk[at])) : 0.f;
-    }
-    for (int i = tid; i < n4 * VT; i += LT_THREADS) {
-        const int t = i / VT, v = i % VT;
-        Vs[i] = (t < n && v < vt) ? lt_silu(ni_to_float(xv[(size_t)(c0 + t) * ld + v])) : 0.f;
-    }
+    lt_load_tile<float, false>(S0, V, D, DP, vt, VT, Ss, VT, nullptr, 0);
+    lt_load_tile<T, true>(proj + (size_t)c0 * ld + (size_t)head * D, ld, n, n4, D, DP, Qs, QS, nullptr, 0);
+    lt_load_tile<T, true>(proj + (size_t)c0 * ld + (size_t)(H + head) * D, ld, n, n4, D, DP, Ks, QS, nullptr, 0);
+    lt_load_tile<T, true>(proj + (size_t)c0 * ld + (size_t)2 * H * D + (size_t)head * V + v0, ld, n, n4, vt, VT, Vs, VT, nullptr, 0);
     __syncthreads();
     // ---- scores: A[t, j] = (q_t . k_j) p[t - j], zero above the diagonal; a thread owns one 4 x 4 tile on or below it
     if (tid < (LT_C / 4) * (LT_C / 4 + 1) / 2) {
@@ -305,21 +340,33 @@ lightning_token_kernel(const T* __restrict__ proj, int ld, float* __restrict__ s
     const float dec = decay[head];
     float* S = state + (size_t)slots[seq] * state_stride + (size_t)head * D * V;
     const bool wide = (V % 4 == 0) && ((reinterpret_cast<size_t>(S) & 15) == 0) && vc + 3 < V;
-    for (int d = warp; d < D; d += LT_THREADS / 32) {
-        float* sp = S + (size_t)d * V + vc;
-        const float k = ks[d], q = qs[d];
-        if (wide) {
-            float4 s4 = *reinterpret_cast<float4*>(sp);
-            s4.x = fmaf(dec, s4.x, k * vv[0]);
-            s4.y = fmaf(dec, s4.y, k * vv[1]);
-            s4.z = fmaf(dec, s4.z, k * vv[2]);
-            s4.w = fmaf(dec, s4.w, k * vv[3]);
-            *reinterpret_cast<float4*>(sp) = s4;
-            acc[0] = fmaf(s4.x, q, acc[0]);
-            acc[1] = fmaf(s4.y, q, acc[1]);
-            acc[2] = fmaf(s4.z, q, acc[2]);
-            acc[3] = fmaf(s4.w, q, acc[3]);
-        } else {
+    constexpr int WARPS = LT_THREADS / 32;
+    if (wide) {
+        for (int d = warp; d < D; d += 4 * WARPS) {          // four rows' loads are under way before the first store
+            float4 s4[4];
+#pragma unroll
+            for (int r = 0; r < 4; ++r)
+                if (d + r * WARPS < D) s4[r] = *reinterpret_cast<const float4*>(S + (size_t)(d + r * WARPS) * V + vc);
+#pragma unroll
+            for (int r = 0; r < 4; ++r) {
+                const int dr = d + r * WARPS;
+                if (dr >= D) break;
+                const float k = ks[dr], q = qs[dr];
+                s4[r].x = fmaf(dec, s4[r].x, k * vv[0]);
+                s4[r].y = fmaf(dec, s4[r].y, k * vv[1]);
+                s4[r].z = fmaf(dec, s4[r].z, k * vv[2]);
+                s4[r].w = fmaf(dec, s4[r].w, k * vv[3]);
+                *reinterpret_cast<float4*>(S + (size_t)dr * V + vc) = s4[r];
+                acc[0] = fmaf(s4[r].x, q, acc[0]);
+                acc[1] = fmaf(s4[r].y, q, acc[1]);
+                acc[2] = fmaf(s4[r].z, q, acc[2]);
+                acc[3] = fmaf(s4[r].w, q, acc[3]);
+            }
+        }
+    } else {
+        for (int d = warp; d < D; d += WARPS) {
+            float* sp = S + (size_t)d * V + vc;
+            const float k = ks[d], q = qs[d];
 #pragma unroll
             for (int b = 0; b < 4; ++b)
                 if (vc + b < V) {
