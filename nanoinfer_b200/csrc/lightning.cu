@@ -23,8 +23,9 @@
 //                                at once
 //
 // and a step of single tokens is one launch (lightning_token_kernel) that reads and writes every state once.
-// All products are register-tiled FP32 FMA loops over shared memory (the design keeps the scores and the state in
-// 32 bits, so no tensor cores).
+// For FP32 projections all products are register-tiled FP32 FMA loops over shared memory.  For bfloat16 projections
+// whose sizes are multiples of 16 the two chunk kernels run on tensor cores (see below), with everything the design
+// keeps in 32 bits split into two bfloat16 halves.
 #include "common.cuh"
 
 #define LT_C 64          // tokens per chunk
@@ -32,6 +33,14 @@
 #define LT_KV_TILE 64    // rows and columns of a chunk's sum that one block of lightning_chunk_kv_kernel owns
 
 __device__ __forceinline__ float lt_silu(float z) { return z / (1.0f + expf(-z)); }
+// The activation of a projection's entry, in the projection's own type: bfloat16 projections give the bfloat16 rounding
+// of silu, in every kernel of this file alike, so that a prompt's portion and single tokens read the same q, k and v.
+template <typename T> __device__ __forceinline__ float lt_act(T raw) { return ni_to_float(ni_from_float<T>(lt_silu(ni_to_float(raw)))); }
+// The fast exponential and division are exact enough for a result that is rounded to 8 bits of mantissa.
+template <> __device__ __forceinline__ float lt_act<__nv_bfloat16>(__nv_bfloat16 raw) {
+    const float z = __bfloat162float(raw);
+    return __bfloat162float(__float2bfloat16_rn(__fdividef(z, 1.0f + __expf(-z))));
+}
 
 // dst[r * dst_stride + c] = f(src[r * ld + c]) * scale[r] for r < rows, c < cols (zero for rows .. rows_pad - 1 and
 // c in cols .. cols_pad - 1).  16 bytes per load when every row starts on 16 bytes and cols is a multiple of the
@@ -54,8 +63,7 @@ __device__ __forceinline__ void lt_load_tile(const T* __restrict__ src, size_t l
                 const float sc = row_scale ? row_scale[scale_last - r] : 1.0f;
 #pragma unroll
                 for (int k = 0; k < VEC; ++k) {
-                    const float z = ni_to_float(e[k]);
-                    v[k] = (SILU ? lt_silu(z) : z) * sc;
+                    v[k] = (SILU ? lt_act<T>(e[k]) : ni_to_float(e[k])) * sc;
                 }
             } else {
 #pragma unroll
@@ -72,8 +80,8 @@ __device__ __forceinline__ void lt_load_tile(const T* __restrict__ src, size_t l
         const int r = i / cols_pad, c = i - r * cols_pad;
         float v = 0.f;
         if (r < rows && c < cols) {
-            const float z = ni_to_float(src[(size_t)r * ld + c]);
-            v = (SILU ? lt_silu(z) : z) * (row_scale ? row_scale[scale_last - r] : 1.0f);
+            const T raw = src[(size_t)r * ld + c];
+            v = (SILU ? lt_act<T>(raw) : ni_to_float(raw)) * (row_scale ? row_scale[scale_last - r] : 1.0f);
         }
         dst[r * dst_stride + c] = v;
     }
@@ -312,6 +320,298 @@ lightning_chunk_out_kernel(const T* __restrict__ proj, int ld, const int* __rest
     }
 }
 
+// ---- bfloat16 projections: the same two chunk kernels on tensor cores ------------------------------------------------
+// mma.sync m16n8k16 (bfloat16 operands, FP32 accumulation).  q, k and v enter as the bfloat16 roundings of their
+// activations.  Whatever the design keeps in 32 bits and a product has to read again - the decayed scores, the state
+// before the chunk, the decayed keys of a chunk's sum - is split into two bfloat16 numbers x = hi + lo (lo the rounding
+// of x - hi), and the product runs once with each: 16 bits of mantissa instead of 8, in FP32 accumulators.
+__device__ __forceinline__ void lt_mma(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+// Four 8 x 8 blocks of 16-bit numbers, each transposed on the way: lane l gives the address of row l % 8 of block l / 8.
+__device__ __forceinline__ void lt_ldsm_x4_trans(uint32_t (&r)[4], const void* p) {
+    const uint32_t addr = (uint32_t)__cvta_generic_to_shared(p);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void lt_split2(float x, float y, uint32_t& hi, uint32_t& lo) {
+    const __nv_bfloat162 h = __floats2bfloat162_rn(x, y);
+    const float2 hf = __bfloat1622float2(h);
+    const __nv_bfloat162 l = __floats2bfloat162_rn(x - hf.x, y - hf.y);
+    hi = *reinterpret_cast<const uint32_t*>(&h);
+    lo = *reinterpret_cast<const uint32_t*>(&l);
+}
+// Rows [0, rows) x columns [0, cols) of src (16-byte loads; cols and cols_pad multiples of 8), through silu, times
+// scale[scale_last - r], into dst_hi (and the remainder into dst_lo if given); zeros up to rows_pad x cols_pad.
+template <int THREADS>
+__device__ __forceinline__ void lt_load_bf16(const __nv_bfloat16* __restrict__ src, size_t ld, int rows, int rows_pad, int cols,
+                                             int cols_pad, __nv_bfloat16* __restrict__ dst_hi, __nv_bfloat16* __restrict__ dst_lo,
+                                             int dst_stride, const float* __restrict__ row_scale, int scale_last) {
+    constexpr int U = 8;                      // loads under way per thread before the first one is used
+    const int per_row = cols_pad / 8, total = rows_pad * per_row;
+    for (int i0 = threadIdx.x; i0 < total; i0 += THREADS * U) {
+        uint4 raw[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int i = i0 + u * THREADS, r = i / per_row, c = (i - r * per_row) * 8;
+            raw[u] = make_uint4(0u, 0u, 0u, 0u);
+            if (i < total && r < rows && c < cols) raw[u] = *reinterpret_cast<const uint4*>(src + (size_t)r * ld + c);
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int i = i0 + u * THREADS, r = i / per_row, c = (i - r * per_row) * 8;
+            if (i >= total) continue;
+            uint4 hi = make_uint4(0u, 0u, 0u, 0u), lo = hi;
+            if (r < rows && c < cols) {
+                const __nv_bfloat16* e = reinterpret_cast<const __nv_bfloat16*>(&raw[u]);
+                const float sc = row_scale ? row_scale[scale_last - r] : 1.0f;
+                float v[8];
+#pragma unroll
+                for (int k = 0; k < 8; ++k) v[k] = lt_act<__nv_bfloat16>(e[k]) * sc;
+                lt_split2(v[0], v[1], hi.x, lo.x);
+                lt_split2(v[2], v[3], hi.y, lo.y);
+                lt_split2(v[4], v[5], hi.z, lo.z);
+                lt_split2(v[6], v[7], hi.w, lo.w);
+            }
+            *reinterpret_cast<uint4*>(dst_hi + r * dst_stride + c) = hi;
+            if (dst_lo) *reinterpret_cast<uint4*>(dst_lo + r * dst_stride + c) = lo;
+        }
+    }
+}
+
+// grid (chunks of the longest request, H, requests); a block owns its chunk's whole sum: a warp 16 rows of it at a time,
+// 64 columns at a time.  D and V multiples of 16.
+__global__ void __launch_bounds__(LT_THREADS)
+lightning_chunk_kv_tc_kernel(const __nv_bfloat16* __restrict__ proj, int ld, const int* __restrict__ cu_q,
+                             const float* __restrict__ decay, float* __restrict__ buf, int H, int D, int V) {
+    extern __shared__ __align__(16) unsigned char lt_raw[];
+    __shared__ float pw[LT_C + 1];
+    __shared__ int base_s;
+    const int KS = D + 8, VS = V + 8;
+    __nv_bfloat16* Khi = reinterpret_cast<__nv_bfloat16*>(lt_raw);      // [LT_C][KS] keys decayed to the chunk's end
+    __nv_bfloat16* Klo = Khi + LT_C * KS;
+    __nv_bfloat16* Vs = Klo + LT_C * KS;                                // [LT_C][VS]
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int chunk = blockIdx.x, head = blockIdx.y, seq = blockIdx.z;
+    const int t0 = cu_q[seq], t1 = cu_q[seq + 1];
+    const int c0 = t0 + chunk * LT_C;
+    if (c0 >= t1) return;
+    const int base = lt_chunk_base(cu_q, seq, &base_s);
+    const int n = min(LT_C, t1 - c0);
+    if (tid == 0) {
+        const float dec = decay[head];
+        float p = 1.0f;
+        for (int i = 0; i <= LT_C; ++i) { pw[i] = p; p *= dec; }
+    }
+    __syncthreads();
+    const __nv_bfloat16* row0 = proj + (size_t)c0 * ld;
+    lt_load_bf16<LT_THREADS>(row0 + (size_t)(H + head) * D, ld, n, LT_C, D, D, Khi, Klo, KS, pw, n - 1);
+    lt_load_bf16<LT_THREADS>(row0 + (size_t)2 * H * D + (size_t)head * V, ld, n, LT_C, V, V, Vs, nullptr, VS, nullptr, 0);
+    __syncthreads();
+    const int g = lane >> 2, tq = lane & 3, blk = lane >> 3, rr = lane & 7;
+    const int k_steps = (n + 15) / 16;
+    float* out = buf + ((size_t)(base + chunk) * H + head) * D * V;
+    for (int mt = warp; mt < D / 16; mt += LT_THREADS / 32) {
+        const int d0 = mt * 16;
+        for (int vb = 0; vb < V; vb += 64) {
+            const int pairs = min(4, (V - vb) / 16);
+            float acc[8][4];
+#pragma unroll
+            for (int a = 0; a < 8; ++a)
+#pragma unroll
+                for (int b = 0; b < 4; ++b) acc[a][b] = 0.f;
+            for (int kt = 0; kt < k_steps; ++kt) {
+                const int j0 = kt * 16;
+                uint32_t ahi[4], alo[4];
+                const int a_off = (j0 + (blk >> 1) * 8 + rr) * KS + d0 + (blk & 1) * 8;
+                lt_ldsm_x4_trans(ahi, Khi + a_off);
+                lt_ldsm_x4_trans(alo, Klo + a_off);
+#pragma unroll
+                for (int np = 0; np < 4; ++np) {
+                    if (np < pairs) {
+                        uint32_t b[4];
+                        lt_ldsm_x4_trans(b, Vs + (j0 + (blk & 1) * 8 + rr) * VS + vb + np * 16 + (blk >> 1) * 8);
+                        lt_mma(acc[2 * np], ahi, b[0], b[1]);
+                        lt_mma(acc[2 * np], alo, b[0], b[1]);
+                        lt_mma(acc[2 * np + 1], ahi, b[2], b[3]);
+                        lt_mma(acc[2 * np + 1], alo, b[2], b[3]);
+                    }
+                }
+            }
+#pragma unroll
+            for (int nt = 0; nt < 8; ++nt) {
+                if (nt < 2 * pairs) {
+                    const int col = vb + nt * 8 + 2 * tq;
+                    *reinterpret_cast<float2*>(out + (size_t)(d0 + g) * V + col) = make_float2(acc[nt][0], acc[nt][1]);
+                    *reinterpret_cast<float2*>(out + (size_t)(d0 + g + 8) * V + col) = make_float2(acc[nt][2], acc[nt][3]);
+                }
+            }
+        }
+    }
+}
+
+// grid (chunks of the longest request x column tiles of VT, H, requests); VT 64 or 128; VT / 64 groups of four warps,
+// a group owns 64 columns, a warp of it 16 tokens of the chunk (the groups compute the same scores).
+template <int VT>
+__global__ void __launch_bounds__(VT * 2)
+lightning_chunk_out_tc_kernel(const __nv_bfloat16* __restrict__ proj, int ld, const int* __restrict__ cu_q,
+                              const float* __restrict__ decay, const float* __restrict__ buf, float* __restrict__ out,
+                              int H, int D, int V, int v_tiles) {
+    extern __shared__ __align__(16) unsigned char lt_raw[];
+    __shared__ float pw[LT_C + 1];
+    __shared__ int base_s;
+    constexpr int VS = VT + 8, LT_OUT_TC_THREADS = VT * 2;
+    const int QS = D + 8;
+    __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(lt_raw);       // [LT_C][QS]
+    __nv_bfloat16* Ks = Qs + LT_C * QS;                                 // [LT_C][QS]
+    __nv_bfloat16* Vs = Ks + LT_C * QS;                                 // [LT_C][VS]
+    __nv_bfloat16* Shi = Vs + LT_C * VS;                                // [D][VS] the state before the chunk
+    __nv_bfloat16* Slo = Shi + D * VS;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int head = blockIdx.y, seq = blockIdx.z;
+    const int chunk = blockIdx.x / v_tiles, v0 = (blockIdx.x % v_tiles) * VT;
+    const int t0 = cu_q[seq], t1 = cu_q[seq + 1];
+    const int c0 = t0 + chunk * LT_C;
+    if (c0 >= t1) return;
+    const int base = lt_chunk_base(cu_q, seq, &base_s);
+    const int n = min(LT_C, t1 - c0);
+    const int vt = min(VT, V - v0);
+    if (tid == 0) {
+        const float dec = decay[head];
+        float p = 1.0f;
+        for (int i = 0; i <= LT_C; ++i) { pw[i] = p; p *= dec; }
+    }
+    const float* S0 = buf + ((size_t)(base + chunk) * H + head) * D * V + v0;
+    for (int i0 = tid; i0 < D * (VT / 4); i0 += LT_OUT_TC_THREADS * 8) {         // eight loads under way per thread
+        float4 s4[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            const int i = i0 + u * LT_OUT_TC_THREADS, r = i / (VT / 4), c = (i % (VT / 4)) * 4;
+            s4[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (r < D && c < vt) s4[u] = *reinterpret_cast<const float4*>(S0 + (size_t)r * V + c);
+        }
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            const int i = i0 + u * LT_OUT_TC_THREADS, r = i / (VT / 4), c = (i % (VT / 4)) * 4;
+            if (r >= D) continue;
+            uint2 hi, lo;
+            lt_split2(s4[u].x, s4[u].y, hi.x, lo.x);
+            lt_split2(s4[u].z, s4[u].w, hi.y, lo.y);
+            *reinterpret_cast<uint2*>(Shi + r * VS + c) = hi;
+            *reinterpret_cast<uint2*>(Slo + r * VS + c) = lo;
+        }
+    }
+    const __nv_bfloat16* row0 = proj + (size_t)c0 * ld;
+    lt_load_bf16<LT_OUT_TC_THREADS>(row0 + (size_t)head * D, ld, n, LT_C, D, D, Qs, nullptr, QS, nullptr, 0);
+    lt_load_bf16<LT_OUT_TC_THREADS>(row0 + (size_t)(H + head) * D, ld, n, LT_C, D, D, Ks, nullptr, QS, nullptr, 0);
+    lt_load_bf16<LT_OUT_TC_THREADS>(row0 + (size_t)2 * H * D + (size_t)head * V + v0, ld, n, LT_C, vt, VT, Vs, nullptr, VS, nullptr, 0);
+    __syncthreads();
+    const int mw = warp & 3, vh = (warp >> 2) * 64;       // the warp's tokens and its columns of the tile
+    const int r0 = mw * 16;
+    if (r0 >= n || vh >= vt) return;
+    const int g = lane >> 2, tq = lane & 3, blk = lane >> 3, rr = lane & 7;
+    const int pairs = min(4, (vt - vh) / 16);
+    // ---- scores of the warp's 16 tokens with the keys up to their diagonal block, decayed and masked
+    float sc[8][4];
+#pragma unroll
+    for (int a = 0; a < 8; ++a)
+#pragma unroll
+        for (int b = 0; b < 4; ++b) sc[a][b] = 0.f;
+    const int nt_end = 2 * mw + 2;
+    for (int kk = 0; kk < D; kk += 16) {
+        uint32_t a[4];
+        const __nv_bfloat16* qp = Qs + (r0 + g) * QS + kk + 2 * tq;
+        a[0] = *reinterpret_cast<const uint32_t*>(qp);
+        a[1] = *reinterpret_cast<const uint32_t*>(qp + 8 * QS);
+        a[2] = *reinterpret_cast<const uint32_t*>(qp + 8);
+        a[3] = *reinterpret_cast<const uint32_t*>(qp + 8 * QS + 8);
+#pragma unroll
+        for (int nt = 0; nt < 8; ++nt) {
+            if (nt < nt_end) {
+                const __nv_bfloat16* kp = Ks + (nt * 8 + g) * QS + kk + 2 * tq;
+                lt_mma(sc[nt], a, *reinterpret_cast<const uint32_t*>(kp), *reinterpret_cast<const uint32_t*>(kp + 8));
+            }
+        }
+    }
+#pragma unroll
+    for (int nt = 0; nt < 8; ++nt)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int t = r0 + g + (i >> 1) * 8, j = nt * 8 + 2 * tq + (i & 1);
+            sc[nt][i] = j <= t ? sc[nt][i] * pw[t - j] : 0.f;
+        }
+    // ---- what the state before the chunk gives: p[t + 1] S0^T q_t
+    float acc[8][4];
+#pragma unroll
+    for (int a = 0; a < 8; ++a)
+#pragma unroll
+        for (int b = 0; b < 4; ++b) acc[a][b] = 0.f;
+    for (int kk = 0; kk < D; kk += 16) {
+        uint32_t a[4];
+        const __nv_bfloat16* qp = Qs + (r0 + g) * QS + kk + 2 * tq;
+        a[0] = *reinterpret_cast<const uint32_t*>(qp);
+        a[1] = *reinterpret_cast<const uint32_t*>(qp + 8 * QS);
+        a[2] = *reinterpret_cast<const uint32_t*>(qp + 8);
+        a[3] = *reinterpret_cast<const uint32_t*>(qp + 8 * QS + 8);
+#pragma unroll
+        for (int np = 0; np < 4; ++np) {
+            if (np < pairs) {
+                const int off = (kk + (blk & 1) * 8 + rr) * VS + vh + np * 16 + (blk >> 1) * 8;
+                uint32_t b[4];
+                lt_ldsm_x4_trans(b, Shi + off);
+                lt_mma(acc[2 * np], a, b[0], b[1]);
+                lt_mma(acc[2 * np + 1], a, b[2], b[3]);
+                lt_ldsm_x4_trans(b, Slo + off);
+                lt_mma(acc[2 * np], a, b[0], b[1]);
+                lt_mma(acc[2 * np + 1], a, b[2], b[3]);
+            }
+        }
+    }
+    {
+        const float p_lo = pw[min(r0 + g + 1, LT_C)], p_hi = pw[min(r0 + g + 9, LT_C)];
+#pragma unroll
+        for (int nt = 0; nt < 8; ++nt) {
+            acc[nt][0] *= p_lo;
+            acc[nt][1] *= p_lo;
+            acc[nt][2] *= p_hi;
+            acc[nt][3] *= p_hi;
+        }
+    }
+    // ---- what the chunk's own tokens give: sum_(j <= t) A[t, j] v_j
+#pragma unroll
+    for (int kt = 0; kt < 4; ++kt) {
+        if (kt <= mw) {
+            uint32_t ahi[4], alo[4];
+            lt_split2(sc[2 * kt][0], sc[2 * kt][1], ahi[0], alo[0]);
+            lt_split2(sc[2 * kt][2], sc[2 * kt][3], ahi[1], alo[1]);
+            lt_split2(sc[2 * kt + 1][0], sc[2 * kt + 1][1], ahi[2], alo[2]);
+            lt_split2(sc[2 * kt + 1][2], sc[2 * kt + 1][3], ahi[3], alo[3]);
+#pragma unroll
+            for (int np = 0; np < 4; ++np) {
+                if (np < pairs) {
+                    uint32_t b[4];
+                    lt_ldsm_x4_trans(b, Vs + (kt * 16 + (blk & 1) * 8 + rr) * VS + vh + np * 16 + (blk >> 1) * 8);
+                    lt_mma(acc[2 * np], ahi, b[0], b[1]);
+                    lt_mma(acc[2 * np], alo, b[0], b[1]);
+                    lt_mma(acc[2 * np + 1], ahi, b[2], b[3]);
+                    lt_mma(acc[2 * np + 1], alo, b[2], b[3]);
+                }
+            }
+        }
+    }
+#pragma unroll
+    for (int nt = 0; nt < 8; ++nt) {
+        if (nt < 2 * pairs) {
+            const int col = v0 + vh + nt * 8 + 2 * tq;
+            const int ta = r0 + g, tb = r0 + g + 8;
+            if (ta < n) *reinterpret_cast<float2*>(out + (size_t)(c0 + ta) * H * V + (size_t)head * V + col) = make_float2(acc[nt][0], acc[nt][1]);
+            if (tb < n) *reinterpret_cast<float2*>(out + (size_t)(c0 + tb) * H * V + (size_t)head * V + col) = make_float2(acc[nt][2], acc[nt][3]);
+        }
+    }
+}
+
 // A step of single tokens: S <- decay S + k v^T, o = S^T q; every state is read and written once.
 // grid (column tiles of 128, H, requests); a warp owns every 8th row, a lane 4 neighbouring columns.
 template <typename T>
@@ -329,13 +629,13 @@ lightning_token_kernel(const T* __restrict__ proj, int ld, float* __restrict__ s
     if (cu_q[seq + 1] <= t) return;
     const T* row = proj + (size_t)t * ld;
     for (int d = tid; d < D; d += LT_THREADS) {
-        qs[d] = lt_silu(ni_to_float(row[(size_t)head * D + d]));
-        ks[d] = lt_silu(ni_to_float(row[(size_t)(H + head) * D + d]));
+        qs[d] = lt_act<T>(row[(size_t)head * D + d]);
+        ks[d] = lt_act<T>(row[(size_t)(H + head) * D + d]);
     }
     const int vc = v0 + lane * 4;
     float vv[4], acc[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-    for (int b = 0; b < 4; ++b) vv[b] = vc + b < V ? lt_silu(ni_to_float(row[(size_t)2 * H * D + (size_t)head * V + vc + b])) : 0.f;
+    for (int b = 0; b < 4; ++b) vv[b] = vc + b < V ? lt_act<T>(row[(size_t)2 * H * D + (size_t)head * V + vc + b]) : 0.f;
     __syncthreads();
     const float dec = decay[head];
     float* S = state + (size_t)slots[seq] * state_stride + (size_t)head * D * V;
@@ -450,6 +750,32 @@ NI_EXPORT int ni_lightning_recurrence(const void* proj, int dtype, int ld, float
     const int d_tiles = (D + LT_KV_TILE - 1) / LT_KV_TILE, kv_tiles = (V + LT_KV_TILE - 1) / LT_KV_TILE, v_tiles = (V + VT - 1) / VT;
     dim3 grid_kv(per_seq * d_tiles * kv_tiles, H, n_seqs), grid_scan((D * V + LT_THREADS - 1) / LT_THREADS, H, n_seqs),
         grid_out(per_seq * v_tiles, H, n_seqs);
+    const bool tc = dtype == NI_DTYPE_BF16 && D % 16 == 0 && V % 16 == 0 && ld % 8 == 0 &&
+                    (reinterpret_cast<size_t>(proj) & 15) == 0 && (reinterpret_cast<size_t>(buf) & 15) == 0 &&
+                    (reinterpret_cast<size_t>(out) & 7) == 0;
+    if (tc) {
+        const size_t smem_kv = ((size_t)2 * LT_C * (D + 8) + (size_t)LT_C * (V + 8)) * sizeof(__nv_bfloat16);
+        const size_t smem_wide = ((size_t)2 * LT_C * (D + 8) + (size_t)LT_C * (128 + 8) + (size_t)2 * D * (128 + 8)) * sizeof(__nv_bfloat16);
+        const int VT = V > 64 && smem_wide <= 160 * 1024 ? 128 : 64;
+        const size_t smem_out = ((size_t)2 * LT_C * (D + 8) + (size_t)LT_C * (VT + 8) + (size_t)2 * D * (VT + 8)) * sizeof(__nv_bfloat16);
+        if (smem_kv <= 200 * 1024 && smem_out <= 200 * 1024) {
+            const int vt_tiles = (V + VT - 1) / VT;
+            const __nv_bfloat16* p = (const __nv_bfloat16*)proj;
+            cudaFuncSetAttribute(lightning_chunk_kv_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_kv);
+            lightning_chunk_kv_tc_kernel<<<dim3(per_seq, H, n_seqs), LT_THREADS, smem_kv, stream>>>(p, ld, cu_q, decay, buf, H, D, V);
+            lightning_scan_kernel<<<grid_scan, LT_THREADS, 0, stream>>>(state, state_stride, cu_q, slots, decay, buf, H, D, V);
+            if (VT == 128) {
+                cudaFuncSetAttribute(lightning_chunk_out_tc_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_out);
+                lightning_chunk_out_tc_kernel<128><<<dim3(per_seq * vt_tiles, H, n_seqs), 256, smem_out, stream>>>(
+                    p, ld, cu_q, decay, buf, out, H, D, V, vt_tiles);
+            } else {
+                cudaFuncSetAttribute(lightning_chunk_out_tc_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_out);
+                lightning_chunk_out_tc_kernel<64><<<dim3(per_seq * vt_tiles, H, n_seqs), 128, smem_out, stream>>>(
+                    p, ld, cu_q, decay, buf, out, H, D, V, vt_tiles);
+            }
+            NI_RETURN_LAUNCH_STATUS();
+        }
+    }
 #define LAUNCH(T)                                                                                                        \
     do {                                                                                                                 \
         lightning_chunk_kv_kernel<T><<<grid_kv, LT_THREADS, 0, stream>>>((const T*)proj, ld, cu_q, decay, buf, H, D, V,  \
