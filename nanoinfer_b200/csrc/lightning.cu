@@ -17,8 +17,8 @@
 // through S, so a step is three launches:
 //
 //   lightning_chunk_kv_kernel    every chunk's own sum_j p[n - 1 - j] k_j v_j^T, all chunks at once, into a buffer
-//   lightning_scan_kernel        per request and head, chunk after chunk: the buffer's entry becomes the state BEFORE
-//                                the chunk, the running state takes the chunk's sum; the last one is the new state
+//   lightning_scan_kernel        per request and head, chunk after chunk: the state BEFORE the chunk goes into the
+//                                buffer's second half, the running state takes the chunk's sum; the last one is the new state
 //   lightning_chunk_out_kernel   every chunk's read-out from its scores, its values and the state before it, all chunks
 //                                at once
 //
@@ -149,10 +149,11 @@ lightning_chunk_kv_kernel(const T* __restrict__ proj, int ld, const int* __restr
             if (d0 + dg + a < D && v0 + vg + b < V) out[(size_t)(d0 + dg + a) * V + v0 + vg + b] = acc[a][b];
 }
 
-// grid (ceil(D V / threads), H, requests)
+// grid (ceil(D V / threads), H, requests).  sums [chunks, H, D, V] in, before [chunks, H, D, V] out: FP32, or with
+// `split` two bfloat16 planes [2, D, V] per chunk and head (hi, then lo = the rounding of the remainder) in the same bytes.
 __global__ void lightning_scan_kernel(float* __restrict__ state, long long state_stride, const int* __restrict__ cu_q,
                                       const int* __restrict__ slots, const float* __restrict__ decay,
-                                      float* __restrict__ buf, int H, int D, int V) {
+                                      const float* __restrict__ sums, float* __restrict__ before, int split, int H, int D, int V) {
     __shared__ int base_s;
     const int head = blockIdx.y, seq = blockIdx.z;
     const int len = cu_q[seq + 1] - cu_q[seq];
@@ -165,8 +166,10 @@ __global__ void lightning_scan_kernel(float* __restrict__ state, long long state
     for (int i = 0; i < LT_C; ++i) p_full *= dec;
     float* S = state + (size_t)slots[seq] * state_stride + (size_t)head * D * V + e;
     float s = *S;
-    const size_t stride = (size_t)H * D * V;
-    float* b = buf + ((size_t)base * H + head) * D * V + e;
+    const size_t stride = (size_t)H * D * V, first = ((size_t)base * H + head) * D * V;
+    const float* b = sums + first + e;
+    float* o32 = before + first + e;
+    __nv_bfloat16* o16 = reinterpret_cast<__nv_bfloat16*>(before + first) + e;
     const int chunks = (len + LT_C - 1) / LT_C;
     for (int c = 0; c < chunks; c += 8) {
         float own[8];                             // loaded together: the chain below waits for memory once per group
@@ -181,7 +184,13 @@ __global__ void lightning_scan_kernel(float* __restrict__ state, long long state
                 pn = 1.0f;
                 for (int k = 0; k < n; ++k) pn *= dec;
             }
-            b[(size_t)(c + i) * stride] = s;       // what the chunk's read-out starts from
+            if (split) {                           // what the chunk's read-out starts from
+                const __nv_bfloat16 hi = __float2bfloat16_rn(s);
+                o16[(size_t)(c + i) * stride * 2] = hi;
+                o16[(size_t)(c + i) * stride * 2 + (size_t)D * V] = __float2bfloat16_rn(s - __bfloat162float(hi));
+            } else {
+                o32[(size_t)(c + i) * stride] = s;
+            }
             s = fmaf(pn, s, own[i]);
         }
     }
@@ -343,44 +352,49 @@ __device__ __forceinline__ void lt_split2(float x, float y, uint32_t& hi, uint32
     hi = *reinterpret_cast<const uint32_t*>(&h);
     lo = *reinterpret_cast<const uint32_t*>(&l);
 }
-// Rows [0, rows) x columns [0, cols) of src (16-byte loads; cols and cols_pad multiples of 8), through silu, times
-// scale[scale_last - r], into dst_hi (and the remainder into dst_lo if given); zeros up to rows_pad x cols_pad.
+__device__ __forceinline__ void lt_cp_async16(void* smem, const void* gmem) {
+    const uint32_t addr = (uint32_t)__cvta_generic_to_shared(smem);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(addr), "l"(gmem));
+}
+__device__ __forceinline__ void lt_cp_async_wait_all() {
+    asm volatile("cp.async.commit_group;\n" ::);
+    asm volatile("cp.async.wait_group 0;\n" ::: "memory");
+}
+// Rows [0, rows) x columns [0, cols) of src copied as they are (asynchronously, 16 bytes a piece) into dst, zeros up to
+// rows_pad x cols_pad; lt_activate_own then turns the pieces that the same thread copied into their activations, in place
+// (times scale[scale_last - r], the remainder of the rounding into dst_lo if given).
 template <int THREADS>
-__device__ __forceinline__ void lt_load_bf16(const __nv_bfloat16* __restrict__ src, size_t ld, int rows, int rows_pad, int cols,
-                                             int cols_pad, __nv_bfloat16* __restrict__ dst_hi, __nv_bfloat16* __restrict__ dst_lo,
-                                             int dst_stride, const float* __restrict__ row_scale, int scale_last) {
-    constexpr int U = 8;                      // loads under way per thread before the first one is used
+__device__ __forceinline__ void lt_copy_raw(const __nv_bfloat16* __restrict__ src, size_t ld, int rows, int rows_pad, int cols,
+                                            int cols_pad, __nv_bfloat16* __restrict__ dst, int dst_stride) {
     const int per_row = cols_pad / 8, total = rows_pad * per_row;
-    for (int i0 = threadIdx.x; i0 < total; i0 += THREADS * U) {
-        uint4 raw[U];
-#pragma unroll
-        for (int u = 0; u < U; ++u) {
-            const int i = i0 + u * THREADS, r = i / per_row, c = (i - r * per_row) * 8;
-            raw[u] = make_uint4(0u, 0u, 0u, 0u);
-            if (i < total && r < rows && c < cols) raw[u] = *reinterpret_cast<const uint4*>(src + (size_t)r * ld + c);
-        }
-#pragma unroll
-        for (int u = 0; u < U; ++u) {
-            const int i = i0 + u * THREADS, r = i / per_row, c = (i - r * per_row) * 8;
-            if (i >= total) continue;
-            uint4 hi = make_uint4(0u, 0u, 0u, 0u), lo = hi;
-            if (r < rows && c < cols) {
-                const __nv_bfloat16* e = reinterpret_cast<const __nv_bfloat16*>(&raw[u]);
-                const float sc = row_scale ? row_scale[scale_last - r] : 1.0f;
-                float v[8];
-#pragma unroll
-                for (int k = 0; k < 8; ++k) v[k] = lt_act<__nv_bfloat16>(e[k]) * sc;
-                lt_split2(v[0], v[1], hi.x, lo.x);
-                lt_split2(v[2], v[3], hi.y, lo.y);
-                lt_split2(v[4], v[5], hi.z, lo.z);
-                lt_split2(v[6], v[7], hi.w, lo.w);
-            }
-            *reinterpret_cast<uint4*>(dst_hi + r * dst_stride + c) = hi;
-            if (dst_lo) *reinterpret_cast<uint4*>(dst_lo + r * dst_stride + c) = lo;
-        }
+    for (int i = threadIdx.x; i < total; i += THREADS) {
+        const int r = i / per_row, c = (i - r * per_row) * 8;
+        if (r < rows && c < cols) lt_cp_async16(dst + r * dst_stride + c, src + (size_t)r * ld + c);
+        else *reinterpret_cast<uint4*>(dst + r * dst_stride + c) = make_uint4(0u, 0u, 0u, 0u);
     }
 }
-
+template <int THREADS>
+__device__ __forceinline__ void lt_activate_own(int rows, int cols, int cols_pad, __nv_bfloat16* __restrict__ dst_hi,
+                                                __nv_bfloat16* __restrict__ dst_lo, int dst_stride,
+                                                const float* __restrict__ row_scale, int scale_last) {
+    const int per_row = cols_pad / 8, total = rows * per_row;
+    for (int i = threadIdx.x; i < total; i += THREADS) {
+        const int r = i / per_row, c = (i - r * per_row) * 8;
+        if (c >= cols) continue;
+        uint4 raw = *reinterpret_cast<const uint4*>(dst_hi + r * dst_stride + c), lo;
+        const __nv_bfloat16* e = reinterpret_cast<const __nv_bfloat16*>(&raw);
+        const float sc = row_scale ? row_scale[scale_last - r] : 1.0f;
+        float v[8];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) v[k] = lt_act<__nv_bfloat16>(e[k]) * sc;
+        lt_split2(v[0], v[1], raw.x, lo.x);
+        lt_split2(v[2], v[3], raw.y, lo.y);
+        lt_split2(v[4], v[5], raw.z, lo.z);
+        lt_split2(v[6], v[7], raw.w, lo.w);
+        *reinterpret_cast<uint4*>(dst_hi + r * dst_stride + c) = raw;
+        if (dst_lo) *reinterpret_cast<uint4*>(dst_lo + r * dst_stride + c) = lo;
+    }
+}
 // grid (chunks of the longest request, H, requests); a block owns its chunk's whole sum: a warp 16 rows of it at a time,
 // 64 columns at a time.  D and V multiples of 16.
 __global__ void __launch_bounds__(LT_THREADS)
@@ -407,8 +421,13 @@ lightning_chunk_kv_tc_kernel(const __nv_bfloat16* __restrict__ proj, int ld, con
     }
     __syncthreads();
     const __nv_bfloat16* row0 = proj + (size_t)c0 * ld;
-    lt_load_bf16<LT_THREADS>(row0 + (size_t)(H + head) * D, ld, n, LT_C, D, D, Khi, Klo, KS, pw, n - 1);
-    lt_load_bf16<LT_THREADS>(row0 + (size_t)2 * H * D + (size_t)head * V, ld, n, LT_C, V, V, Vs, nullptr, VS, nullptr, 0);
+    lt_copy_raw<LT_THREADS>(row0 + (size_t)(H + head) * D, ld, n, LT_C, D, D, Khi, KS);
+    lt_copy_raw<LT_THREADS>(row0 + (size_t)2 * H * D + (size_t)head * V, ld, n, LT_C, V, V, Vs, VS);
+    for (int i = tid; i < (LT_C - n) * (D / 8); i += LT_THREADS)          // the rows beyond the chunk's tokens
+        *reinterpret_cast<uint4*>(Klo + (n + i / (D / 8)) * KS + (i % (D / 8)) * 8) = make_uint4(0u, 0u, 0u, 0u);
+    lt_cp_async_wait_all();
+    lt_activate_own<LT_THREADS>(n, D, D, Khi, Klo, KS, pw, n - 1);
+    lt_activate_own<LT_THREADS>(n, V, V, Vs, nullptr, VS, nullptr, 0);
     __syncthreads();
     const int g = lane >> 2, tq = lane & 3, blk = lane >> 3, rr = lane & 7;
     const int k_steps = (n + 15) / 16;
@@ -428,15 +447,32 @@ lightning_chunk_kv_tc_kernel(const __nv_bfloat16* __restrict__ proj, int ld, con
                 const int a_off = (j0 + (blk >> 1) * 8 + rr) * KS + d0 + (blk & 1) * 8;
                 lt_ldsm_x4_trans(ahi, Khi + a_off);
                 lt_ldsm_x4_trans(alo, Klo + a_off);
+                const __nv_bfloat16* vp = Vs + (j0 + (blk & 1) * 8 + rr) * VS + vb + (blk >> 1) * 8;
+                if (pairs == 4) {                               // a whole block of 64 columns: no checks between the loads
+                    uint32_t b[4][4];
 #pragma unroll
-                for (int np = 0; np < 4; ++np) {
-                    if (np < pairs) {
-                        uint32_t b[4];
-                        lt_ldsm_x4_trans(b, Vs + (j0 + (blk & 1) * 8 + rr) * VS + vb + np * 16 + (blk >> 1) * 8);
-                        lt_mma(acc[2 * np], ahi, b[0], b[1]);
-                        lt_mma(acc[2 * np], alo, b[0], b[1]);
-                        lt_mma(acc[2 * np + 1], ahi, b[2], b[3]);
-                        lt_mma(acc[2 * np + 1], alo, b[2], b[3]);
+                    for (int np = 0; np < 4; ++np) lt_ldsm_x4_trans(b[np], vp + np * 16);
+#pragma unroll
+                    for (int np = 0; np < 4; ++np) {
+                        lt_mma(acc[2 * np], ahi, b[np][0], b[np][1]);
+                        lt_mma(acc[2 * np + 1], ahi, b[np][2], b[np][3]);
+                    }
+#pragma unroll
+                    for (int np = 0; np < 4; ++np) {
+                        lt_mma(acc[2 * np], alo, b[np][0], b[np][1]);
+                        lt_mma(acc[2 * np + 1], alo, b[np][2], b[np][3]);
+                    }
+                } else {
+#pragma unroll
+                    for (int np = 0; np < 4; ++np) {
+                        if (np < pairs) {
+                            uint32_t b[4];
+                            lt_ldsm_x4_trans(b, vp + np * 16);
+                            lt_mma(acc[2 * np], ahi, b[0], b[1]);
+                            lt_mma(acc[2 * np], alo, b[0], b[1]);
+                            lt_mma(acc[2 * np + 1], ahi, b[2], b[3]);
+                            lt_mma(acc[2 * np + 1], alo, b[2], b[3]);
+                        }
                     }
                 }
             }
@@ -452,74 +488,21 @@ lightning_chunk_kv_tc_kernel(const __nv_bfloat16* __restrict__ proj, int ld, con
     }
 }
 
-// grid (chunks of the longest request x column tiles of VT, H, requests); VT 64 or 128; VT / 64 groups of four warps,
-// a group owns 64 columns, a warp of it 16 tokens of the chunk (the groups compute the same scores).
-template <int VT>
-__global__ void __launch_bounds__(VT * 2)
-lightning_chunk_out_tc_kernel(const __nv_bfloat16* __restrict__ proj, int ld, const int* __restrict__ cu_q,
-                              const float* __restrict__ decay, const float* __restrict__ buf, float* __restrict__ out,
-                              int H, int D, int V, int v_tiles) {
-    extern __shared__ __align__(16) unsigned char lt_raw[];
-    __shared__ float pw[LT_C + 1];
-    __shared__ int base_s;
-    constexpr int VS = VT + 8, LT_OUT_TC_THREADS = VT * 2;
-    const int QS = D + 8;
-    __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(lt_raw);       // [LT_C][QS]
-    __nv_bfloat16* Ks = Qs + LT_C * QS;                                 // [LT_C][QS]
-    __nv_bfloat16* Vs = Ks + LT_C * QS;                                 // [LT_C][VS]
-    __nv_bfloat16* Shi = Vs + LT_C * VS;                                // [D][VS] the state before the chunk
-    __nv_bfloat16* Slo = Shi + D * VS;
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int head = blockIdx.y, seq = blockIdx.z;
-    const int chunk = blockIdx.x / v_tiles, v0 = (blockIdx.x % v_tiles) * VT;
-    const int t0 = cu_q[seq], t1 = cu_q[seq + 1];
-    const int c0 = t0 + chunk * LT_C;
-    if (c0 >= t1) return;
-    const int base = lt_chunk_base(cu_q, seq, &base_s);
-    const int n = min(LT_C, t1 - c0);
-    const int vt = min(VT, V - v0);
-    if (tid == 0) {
-        const float dec = decay[head];
-        float p = 1.0f;
-        for (int i = 0; i <= LT_C; ++i) { pw[i] = p; p *= dec; }
-    }
-    const float* S0 = buf + ((size_t)(base + chunk) * H + head) * D * V + v0;
-    for (int i0 = tid; i0 < D * (VT / 4); i0 += LT_OUT_TC_THREADS * 8) {         // eight loads under way per thread
-        float4 s4[8];
-#pragma unroll
-        for (int u = 0; u < 8; ++u) {
-            const int i = i0 + u * LT_OUT_TC_THREADS, r = i / (VT / 4), c = (i % (VT / 4)) * 4;
-            s4[u] = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (r < D && c < vt) s4[u] = *reinterpret_cast<const float4*>(S0 + (size_t)r * V + c);
-        }
-#pragma unroll
-        for (int u = 0; u < 8; ++u) {
-            const int i = i0 + u * LT_OUT_TC_THREADS, r = i / (VT / 4), c = (i % (VT / 4)) * 4;
-            if (r >= D) continue;
-            uint2 hi, lo;
-            lt_split2(s4[u].x, s4[u].y, hi.x, lo.x);
-            lt_split2(s4[u].z, s4[u].w, hi.y, lo.y);
-            *reinterpret_cast<uint2*>(Shi + r * VS + c) = hi;
-            *reinterpret_cast<uint2*>(Slo + r * VS + c) = lo;
-        }
-    }
-    const __nv_bfloat16* row0 = proj + (size_t)c0 * ld;
-    lt_load_bf16<LT_OUT_TC_THREADS>(row0 + (size_t)head * D, ld, n, LT_C, D, D, Qs, nullptr, QS, nullptr, 0);
-    lt_load_bf16<LT_OUT_TC_THREADS>(row0 + (size_t)(H + head) * D, ld, n, LT_C, D, D, Ks, nullptr, QS, nullptr, 0);
-    lt_load_bf16<LT_OUT_TC_THREADS>(row0 + (size_t)2 * H * D + (size_t)head * V + v0, ld, n, LT_C, vt, VT, Vs, nullptr, VS, nullptr, 0);
-    __syncthreads();
-    const int mw = warp & 3, vh = (warp >> 2) * 64;       // the warp's tokens and its columns of the tile
-    const int r0 = mw * 16;
-    if (r0 >= n || vh >= vt) return;
-    const int g = lane >> 2, tq = lane & 3, blk = lane >> 3, rr = lane & 7;
-    const int pairs = min(4, (vt - vh) / 16);
+// What one warp of lightning_chunk_out_tc_kernel does after the loads: tokens MW * 16 .. MW * 16 + 15 of the chunk, columns
+// vh .. vh + 16 pairs - 1 of the block's tile (FULL: all 64, no checks inside the loops).
+template <int MW, bool FULL>
+__device__ __forceinline__ void lt_out_warp(const __nv_bfloat16* __restrict__ Qs, const __nv_bfloat16* __restrict__ Ks,
+                                            const __nv_bfloat16* __restrict__ Vs, const __nv_bfloat16* __restrict__ Shi,
+                                            const __nv_bfloat16* __restrict__ Slo, const float* __restrict__ pw, int QS, int VS,
+                                            int D, int vh, int pairs, int n, float* __restrict__ out, size_t out_stride) {
+    const int lane = threadIdx.x & 31, g = lane >> 2, tq = lane & 3, blk = lane >> 3, rr = lane & 7;
+    constexpr int r0 = MW * 16;
     // ---- scores of the warp's 16 tokens with the keys up to their diagonal block, decayed and masked
     float sc[8][4];
 #pragma unroll
     for (int a = 0; a < 8; ++a)
 #pragma unroll
         for (int b = 0; b < 4; ++b) sc[a][b] = 0.f;
-    const int nt_end = 2 * mw + 2;
     for (int kk = 0; kk < D; kk += 16) {
         uint32_t a[4];
         const __nv_bfloat16* qp = Qs + (r0 + g) * QS + kk + 2 * tq;
@@ -529,7 +512,7 @@ lightning_chunk_out_tc_kernel(const __nv_bfloat16* __restrict__ proj, int ld, co
         a[3] = *reinterpret_cast<const uint32_t*>(qp + 8 * QS + 8);
 #pragma unroll
         for (int nt = 0; nt < 8; ++nt) {
-            if (nt < nt_end) {
+            if (nt < 2 * MW + 2) {
                 const __nv_bfloat16* kp = Ks + (nt * 8 + g) * QS + kk + 2 * tq;
                 lt_mma(sc[nt], a, *reinterpret_cast<const uint32_t*>(kp), *reinterpret_cast<const uint32_t*>(kp + 8));
             }
@@ -557,7 +540,7 @@ lightning_chunk_out_tc_kernel(const __nv_bfloat16* __restrict__ proj, int ld, co
         a[3] = *reinterpret_cast<const uint32_t*>(qp + 8 * QS + 8);
 #pragma unroll
         for (int np = 0; np < 4; ++np) {
-            if (np < pairs) {
+            if (FULL || np < pairs) {
                 const int off = (kk + (blk & 1) * 8 + rr) * VS + vh + np * 16 + (blk >> 1) * 8;
                 uint32_t b[4];
                 lt_ldsm_x4_trans(b, Shi + off);
@@ -582,7 +565,7 @@ lightning_chunk_out_tc_kernel(const __nv_bfloat16* __restrict__ proj, int ld, co
     // ---- what the chunk's own tokens give: sum_(j <= t) A[t, j] v_j
 #pragma unroll
     for (int kt = 0; kt < 4; ++kt) {
-        if (kt <= mw) {
+        if (kt <= MW) {
             uint32_t ahi[4], alo[4];
             lt_split2(sc[2 * kt][0], sc[2 * kt][1], ahi[0], alo[0]);
             lt_split2(sc[2 * kt][2], sc[2 * kt][3], ahi[1], alo[1]);
@@ -590,7 +573,7 @@ lightning_chunk_out_tc_kernel(const __nv_bfloat16* __restrict__ proj, int ld, co
             lt_split2(sc[2 * kt + 1][2], sc[2 * kt + 1][3], ahi[3], alo[3]);
 #pragma unroll
             for (int np = 0; np < 4; ++np) {
-                if (np < pairs) {
+                if (FULL || np < pairs) {
                     uint32_t b[4];
                     lt_ldsm_x4_trans(b, Vs + (kt * 16 + (blk & 1) * 8 + rr) * VS + vh + np * 16 + (blk >> 1) * 8);
                     lt_mma(acc[2 * np], ahi, b[0], b[1]);
@@ -603,13 +586,72 @@ lightning_chunk_out_tc_kernel(const __nv_bfloat16* __restrict__ proj, int ld, co
     }
 #pragma unroll
     for (int nt = 0; nt < 8; ++nt) {
-        if (nt < 2 * pairs) {
-            const int col = v0 + vh + nt * 8 + 2 * tq;
+        if (FULL || nt < 2 * pairs) {
+            const int col = vh + nt * 8 + 2 * tq;
             const int ta = r0 + g, tb = r0 + g + 8;
-            if (ta < n) *reinterpret_cast<float2*>(out + (size_t)(c0 + ta) * H * V + (size_t)head * V + col) = make_float2(acc[nt][0], acc[nt][1]);
-            if (tb < n) *reinterpret_cast<float2*>(out + (size_t)(c0 + tb) * H * V + (size_t)head * V + col) = make_float2(acc[nt][2], acc[nt][3]);
+            if (ta < n) *reinterpret_cast<float2*>(out + (size_t)ta * out_stride + col) = make_float2(acc[nt][0], acc[nt][1]);
+            if (tb < n) *reinterpret_cast<float2*>(out + (size_t)tb * out_stride + col) = make_float2(acc[nt][2], acc[nt][3]);
         }
     }
+}
+
+// grid (chunks of the longest request x column tiles of VT, H, requests); VT 64 or 128; VT / 64 groups of four warps,
+// a group owns 64 columns, a warp of it 16 tokens of the chunk (the groups compute the same scores).
+template <int VT>
+__global__ void __launch_bounds__(VT * 2)
+lightning_chunk_out_tc_kernel(const __nv_bfloat16* __restrict__ proj, int ld, const int* __restrict__ cu_q,
+                              const float* __restrict__ decay, const float* __restrict__ buf, float* __restrict__ out,
+                              int H, int D, int V, int v_tiles) {
+    extern __shared__ __align__(16) unsigned char lt_raw[];
+    __shared__ float pw[LT_C + 1];
+    __shared__ int base_s;
+    constexpr int VS = VT + 8, LT_OUT_TC_THREADS = VT * 2;
+    const int QS = D + 8;
+    __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(lt_raw);       // [LT_C][QS]
+    __nv_bfloat16* Ks = Qs + LT_C * QS;                                 // [LT_C][QS]
+    __nv_bfloat16* Vs = Ks + LT_C * QS;                                 // [LT_C][VS]
+    __nv_bfloat16* Shi = Vs + LT_C * VS;                                // [D][VS] the state before the chunk
+    __nv_bfloat16* Slo = Shi + D * VS;
+    const int tid = threadIdx.x, warp = tid >> 5;
+    const int head = blockIdx.y, seq = blockIdx.z;
+    const int chunk = blockIdx.x / v_tiles, v0 = (blockIdx.x % v_tiles) * VT;
+    const int t0 = cu_q[seq], t1 = cu_q[seq + 1];
+    const int c0 = t0 + chunk * LT_C;
+    if (c0 >= t1) return;
+    const int base = lt_chunk_base(cu_q, seq, &base_s);
+    const int n = min(LT_C, t1 - c0);
+    const int vt = min(VT, V - v0);
+    if (tid == 0) {
+        const float dec = decay[head];
+        float p = 1.0f;
+        for (int i = 0; i <= LT_C; ++i) { pw[i] = p; p *= dec; }
+    }
+    const __nv_bfloat16* S0 = reinterpret_cast<const __nv_bfloat16*>(buf + ((size_t)(base + chunk) * H + head) * D * V) + v0;
+    const __nv_bfloat16* row0 = proj + (size_t)c0 * ld;
+    lt_copy_raw<LT_OUT_TC_THREADS>(row0 + (size_t)head * D, ld, n, LT_C, D, D, Qs, QS);
+    lt_copy_raw<LT_OUT_TC_THREADS>(row0 + (size_t)(H + head) * D, ld, n, LT_C, D, D, Ks, QS);
+    lt_copy_raw<LT_OUT_TC_THREADS>(row0 + (size_t)2 * H * D + (size_t)head * V + v0, ld, n, LT_C, vt, VT, Vs, VS);
+    lt_copy_raw<LT_OUT_TC_THREADS>(S0, V, D, D, vt, VT, Shi, VS);                  // the two planes of the state before
+    lt_copy_raw<LT_OUT_TC_THREADS>(S0 + (size_t)D * V, V, D, D, vt, VT, Slo, VS);
+    lt_cp_async_wait_all();
+    lt_activate_own<LT_OUT_TC_THREADS>(n, D, D, Qs, nullptr, QS, nullptr, 0);
+    lt_activate_own<LT_OUT_TC_THREADS>(n, D, D, Ks, nullptr, QS, nullptr, 0);
+    lt_activate_own<LT_OUT_TC_THREADS>(n, vt, VT, Vs, nullptr, VS, nullptr, 0);
+    __syncthreads();
+    const int mw = warp & 3, vh = (warp >> 2) * 64;       // the warp's tokens and its columns of the tile
+    if (mw * 16 >= n || vh >= vt) return;
+    const int pairs = min(4, (vt - vh) / 16);
+    float* o = out + (size_t)c0 * H * V + (size_t)head * V + v0;
+#define LT_OUT_WARP(MW)                                                                                                  \
+    do {                                                                                                                 \
+        if (pairs == 4) lt_out_warp<MW, true>(Qs, Ks, Vs, Shi, Slo, pw, QS, VS, D, vh, pairs, n, o, (size_t)H * V);      \
+        else lt_out_warp<MW, false>(Qs, Ks, Vs, Shi, Slo, pw, QS, VS, D, vh, pairs, n, o, (size_t)H * V);                \
+    } while (0)
+    if (mw == 0) LT_OUT_WARP(0);
+    else if (mw == 1) LT_OUT_WARP(1);
+    else if (mw == 2) LT_OUT_WARP(2);
+    else LT_OUT_WARP(3);
+#undef LT_OUT_WARP
 }
 
 // A step of single tokens: S <- decay S + k v^T, o = S^T q; every state is read and written once.
@@ -712,15 +754,17 @@ static size_t lt_out_smem_bytes(int D, int VT) {
 }
 
 // The most chunks that requests of n_tokens tokens in all can have.
-NI_EXPORT int ni_lightning_max_chunks(int n_tokens, int n_seqs) {
+static long long lt_chunks(int n_tokens, int n_seqs) {
     const long long whole = (long long)n_tokens / LT_C + n_seqs;
-    return whole < n_tokens ? (int)whole : n_tokens;
+    return whole < n_tokens ? whole : n_tokens;
 }
+// The buffer of a step in units of H D V floats: every chunk's own sum, and the state before every chunk.
+NI_EXPORT int ni_lightning_max_chunks(int n_tokens, int n_seqs) { return (int)(2 * lt_chunks(n_tokens, n_seqs)); }
 
 // proj [T, ld] with columns q (H D) | k (H D) | v (H V) | ...; state FP32 [slots, state_stride] holding S [H, D, V] of
 // every request; decay FP32 [H]; out FP32 [T, H V].  The state advances by the step's tokens.  max_q_len: the most
 // tokens that one request brings (1: a step of single tokens, which needs no buffer); buf FP32 with room for
-// buf_chunks x H D V, at least ni_lightning_max_chunks(n_tokens, n_seqs) chunks.
+// buf_chunks x H D V, at least ni_lightning_max_chunks(n_tokens, n_seqs) of them.
 NI_EXPORT int ni_lightning_recurrence(const void* proj, int dtype, int ld, float* state, long long state_stride,
                                       const int* cu_q, const int* slots, const float* decay, float* out, int n_tokens,
                                       int n_seqs, int max_q_len, float* buf, long long buf_chunks, int H, int D, int V,
@@ -743,6 +787,7 @@ NI_EXPORT int ni_lightning_recurrence(const void* proj, int dtype, int ld, float
         NI_RETURN_LAUNCH_STATUS();
     }
     if (buf == nullptr || buf_chunks < ni_lightning_max_chunks(n_tokens, n_seqs)) return NI_ERR_BAD_ARGUMENT;
+    float* before = buf + (size_t)lt_chunks(n_tokens, n_seqs) * H * D * V;      // the second half: the state before every chunk
     const int VT = D <= 128 ? 64 : 32;
     const size_t smem = lt_out_smem_bytes(D, VT);
     if (smem > 227 * 1024) return NI_ERR_UNSUPPORTED_SIZE;
@@ -763,15 +808,15 @@ NI_EXPORT int ni_lightning_recurrence(const void* proj, int dtype, int ld, float
             const __nv_bfloat16* p = (const __nv_bfloat16*)proj;
             cudaFuncSetAttribute(lightning_chunk_kv_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_kv);
             lightning_chunk_kv_tc_kernel<<<dim3(per_seq, H, n_seqs), LT_THREADS, smem_kv, stream>>>(p, ld, cu_q, decay, buf, H, D, V);
-            lightning_scan_kernel<<<grid_scan, LT_THREADS, 0, stream>>>(state, state_stride, cu_q, slots, decay, buf, H, D, V);
+            lightning_scan_kernel<<<grid_scan, LT_THREADS, 0, stream>>>(state, state_stride, cu_q, slots, decay, buf, before, 1, H, D, V);
             if (VT == 128) {
                 cudaFuncSetAttribute(lightning_chunk_out_tc_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_out);
                 lightning_chunk_out_tc_kernel<128><<<dim3(per_seq * vt_tiles, H, n_seqs), 256, smem_out, stream>>>(
-                    p, ld, cu_q, decay, buf, out, H, D, V, vt_tiles);
+                    p, ld, cu_q, decay, before, out, H, D, V, vt_tiles);
             } else {
                 cudaFuncSetAttribute(lightning_chunk_out_tc_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_out);
                 lightning_chunk_out_tc_kernel<64><<<dim3(per_seq * vt_tiles, H, n_seqs), 128, smem_out, stream>>>(
-                    p, ld, cu_q, decay, buf, out, H, D, V, vt_tiles);
+                    p, ld, cu_q, decay, before, out, H, D, V, vt_tiles);
             }
             NI_RETURN_LAUNCH_STATUS();
         }
@@ -780,14 +825,14 @@ NI_EXPORT int ni_lightning_recurrence(const void* proj, int dtype, int ld, float
     do {                                                                                                                 \
         lightning_chunk_kv_kernel<T><<<grid_kv, LT_THREADS, 0, stream>>>((const T*)proj, ld, cu_q, decay, buf, H, D, V,  \
                                                                          d_tiles, kv_tiles);                             \
-        lightning_scan_kernel<<<grid_scan, LT_THREADS, 0, stream>>>(state, state_stride, cu_q, slots, decay, buf, H, D, V); \
+        lightning_scan_kernel<<<grid_scan, LT_THREADS, 0, stream>>>(state, state_stride, cu_q, slots, decay, buf, before, 0, H, D, V); \
         if (VT == 64) {                                                                                                  \
             cudaFuncSetAttribute(lightning_chunk_out_kernel<T, 64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
-            lightning_chunk_out_kernel<T, 64><<<grid_out, LT_THREADS, smem, stream>>>((const T*)proj, ld, cu_q, decay, buf, \
+            lightning_chunk_out_kernel<T, 64><<<grid_out, LT_THREADS, smem, stream>>>((const T*)proj, ld, cu_q, decay, before, \
                                                                                       out, H, D, V, v_tiles);            \
         } else {                                                                                                         \
             cudaFuncSetAttribute(lightning_chunk_out_kernel<T, 32>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
-            lightning_chunk_out_kernel<T, 32><<<grid_out, LT_THREADS, smem, stream>>>((const T*)proj, ld, cu_q, decay, buf, \
+            lightning_chunk_out_kernel<T, 32><<<grid_out, LT_THREADS, smem, stream>>>((const T*)proj, ld, cu_q, decay, before, \
                                                                                       out, H, D, V, v_tiles);            \
         }                                                                                                                \
     } while (0)
