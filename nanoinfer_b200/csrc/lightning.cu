@@ -356,31 +356,40 @@ __device__ __forceinline__ void lt_cp_async16(void* smem, const void* gmem) {
     const uint32_t addr = (uint32_t)__cvta_generic_to_shared(smem);
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(addr), "l"(gmem));
 }
-__device__ __forceinline__ void lt_cp_async_wait_all() {
-    asm volatile("cp.async.commit_group;\n" ::);
-    asm volatile("cp.async.wait_group 0;\n" ::: "memory");
-}
+__device__ __forceinline__ void lt_cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+// Waits until at most N of the thread's committed groups are still under way.
+template <int N> __device__ __forceinline__ void lt_cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory"); }
 // Rows [0, rows) x columns [0, cols) of src copied as they are (asynchronously, 16 bytes a piece) into dst, zeros up to
 // rows_pad x cols_pad; lt_activate_own then turns the pieces that the same thread copied into their activations, in place
 // (times scale[scale_last - r], the remainder of the rounding into dst_lo if given).
+// Calls piece(r, c) for every 8-number piece (row r, first column c) of rows x cols_pad, thread by thread; the same thread
+// gets the same pieces in every call with the same sizes.  When a row's pieces divide the block, a thread keeps its
+// column and steps down the rows (no division per piece).
+template <int THREADS, typename F>
+__device__ __forceinline__ void lt_for_pieces(int rows, int cols_pad, F piece) {
+    const int per_row = cols_pad / 8;
+    if (THREADS % per_row == 0) {
+        const int c = (threadIdx.x % per_row) * 8, dr = THREADS / per_row;
+#pragma unroll 4
+        for (int r = threadIdx.x / per_row; r < rows; r += dr) piece(r, c);
+    } else {
+        for (int i = threadIdx.x; i < rows * per_row; i += THREADS) piece(i / per_row, (i % per_row) * 8);
+    }
+}
 template <int THREADS>
 __device__ __forceinline__ void lt_copy_raw(const __nv_bfloat16* __restrict__ src, size_t ld, int rows, int rows_pad, int cols,
                                             int cols_pad, __nv_bfloat16* __restrict__ dst, int dst_stride) {
-    const int per_row = cols_pad / 8, total = rows_pad * per_row;
-    for (int i = threadIdx.x; i < total; i += THREADS) {
-        const int r = i / per_row, c = (i - r * per_row) * 8;
+    lt_for_pieces<THREADS>(rows_pad, cols_pad, [&](int r, int c) {
         if (r < rows && c < cols) lt_cp_async16(dst + r * dst_stride + c, src + (size_t)r * ld + c);
         else *reinterpret_cast<uint4*>(dst + r * dst_stride + c) = make_uint4(0u, 0u, 0u, 0u);
-    }
+    });
 }
 template <int THREADS>
 __device__ __forceinline__ void lt_activate_own(int rows, int cols, int cols_pad, __nv_bfloat16* __restrict__ dst_hi,
                                                 __nv_bfloat16* __restrict__ dst_lo, int dst_stride,
                                                 const float* __restrict__ row_scale, int scale_last) {
-    const int per_row = cols_pad / 8, total = rows * per_row;
-    for (int i = threadIdx.x; i < total; i += THREADS) {
-        const int r = i / per_row, c = (i - r * per_row) * 8;
-        if (c >= cols) continue;
+    lt_for_pieces<THREADS>(rows, cols_pad, [&](int r, int c) {
+        if (c >= cols) return;
         uint4 raw = *reinterpret_cast<const uint4*>(dst_hi + r * dst_stride + c), lo;
         const __nv_bfloat16* e = reinterpret_cast<const __nv_bfloat16*>(&raw);
         const float sc = row_scale ? row_scale[scale_last - r] : 1.0f;
@@ -393,8 +402,9 @@ __device__ __forceinline__ void lt_activate_own(int rows, int cols, int cols_pad
         lt_split2(v[6], v[7], raw.w, lo.w);
         *reinterpret_cast<uint4*>(dst_hi + r * dst_stride + c) = raw;
         if (dst_lo) *reinterpret_cast<uint4*>(dst_lo + r * dst_stride + c) = lo;
-    }
+    });
 }
+
 // grid (chunks of the longest request, H, requests); a block owns its chunk's whole sum: a warp 16 rows of it at a time,
 // 64 columns at a time.  D and V multiples of 16.
 __global__ void __launch_bounds__(LT_THREADS)
@@ -422,11 +432,14 @@ lightning_chunk_kv_tc_kernel(const __nv_bfloat16* __restrict__ proj, int ld, con
     __syncthreads();
     const __nv_bfloat16* row0 = proj + (size_t)c0 * ld;
     lt_copy_raw<LT_THREADS>(row0 + (size_t)(H + head) * D, ld, n, LT_C, D, D, Khi, KS);
+    lt_cp_async_commit();
     lt_copy_raw<LT_THREADS>(row0 + (size_t)2 * H * D + (size_t)head * V, ld, n, LT_C, V, V, Vs, VS);
+    lt_cp_async_commit();
     for (int i = tid; i < (LT_C - n) * (D / 8); i += LT_THREADS)          // the rows beyond the chunk's tokens
         *reinterpret_cast<uint4*>(Klo + (n + i / (D / 8)) * KS + (i % (D / 8)) * 8) = make_uint4(0u, 0u, 0u, 0u);
-    lt_cp_async_wait_all();
+    lt_cp_async_wait<1>();                                 // the keys are here; the values are still under way
     lt_activate_own<LT_THREADS>(n, D, D, Khi, Klo, KS, pw, n - 1);
+    lt_cp_async_wait<0>();
     lt_activate_own<LT_THREADS>(n, V, V, Vs, nullptr, VS, nullptr, 0);
     __syncthreads();
     const int g = lane >> 2, tq = lane & 3, blk = lane >> 3, rr = lane & 7;
@@ -631,12 +644,15 @@ lightning_chunk_out_tc_kernel(const __nv_bfloat16* __restrict__ proj, int ld, co
     lt_copy_raw<LT_OUT_TC_THREADS>(row0 + (size_t)head * D, ld, n, LT_C, D, D, Qs, QS);
     lt_copy_raw<LT_OUT_TC_THREADS>(row0 + (size_t)(H + head) * D, ld, n, LT_C, D, D, Ks, QS);
     lt_copy_raw<LT_OUT_TC_THREADS>(row0 + (size_t)2 * H * D + (size_t)head * V + v0, ld, n, LT_C, vt, VT, Vs, VS);
+    lt_cp_async_commit();
     lt_copy_raw<LT_OUT_TC_THREADS>(S0, V, D, D, vt, VT, Shi, VS);                  // the two planes of the state before
     lt_copy_raw<LT_OUT_TC_THREADS>(S0 + (size_t)D * V, V, D, D, vt, VT, Slo, VS);
-    lt_cp_async_wait_all();
+    lt_cp_async_commit();
+    lt_cp_async_wait<1>();                                 // q, k, v are here; the state's planes are still under way
     lt_activate_own<LT_OUT_TC_THREADS>(n, D, D, Qs, nullptr, QS, nullptr, 0);
     lt_activate_own<LT_OUT_TC_THREADS>(n, D, D, Ks, nullptr, QS, nullptr, 0);
     lt_activate_own<LT_OUT_TC_THREADS>(n, vt, VT, Vs, nullptr, VS, nullptr, 0);
+    lt_cp_async_wait<0>();
     __syncthreads();
     const int mw = warp & 3, vh = (warp >> 2) * 64;       // the warp's tokens and its columns of the tile
     if (mw * 16 >= n || vh >= vt) return;
