@@ -501,21 +501,14 @@ lightning_chunk_kv_tc_kernel(const __nv_bfloat16* __restrict__ proj, int ld, con
     }
 }
 
-// What one warp of lightning_chunk_out_tc_kernel does after the loads: tokens MW * 16 .. MW * 16 + 15 of the chunk, columns
+// The three phases of one warp of lightning_chunk_out_tc_kernel: tokens MW * 16 .. MW * 16 + 15 of the chunk, columns
 // vh .. vh + 16 pairs - 1 of the block's tile (FULL: all 64, no checks inside the loops).
-template <int MW, bool FULL>
-__device__ __forceinline__ void lt_out_warp(const __nv_bfloat16* __restrict__ Qs, const __nv_bfloat16* __restrict__ Ks,
-                                            const __nv_bfloat16* __restrict__ Vs, const __nv_bfloat16* __restrict__ Shi,
-                                            const __nv_bfloat16* __restrict__ Slo, const float* __restrict__ pw, int QS, int VS,
-                                            int D, int vh, int pairs, int n, float* __restrict__ out, size_t out_stride) {
-    const int lane = threadIdx.x & 31, g = lane >> 2, tq = lane & 3, blk = lane >> 3, rr = lane & 7;
+// Scores of the warp's 16 tokens with the keys up to their diagonal block, decayed and masked.
+template <int MW>
+__device__ __forceinline__ void lt_out_scores(const __nv_bfloat16* __restrict__ Qs, const __nv_bfloat16* __restrict__ Ks,
+                                              const float* __restrict__ pw, int QS, int D, float (&sc)[8][4]) {
+    const int lane = threadIdx.x & 31, g = lane >> 2, tq = lane & 3;
     constexpr int r0 = MW * 16;
-    // ---- scores of the warp's 16 tokens with the keys up to their diagonal block, decayed and masked
-    float sc[8][4];
-#pragma unroll
-    for (int a = 0; a < 8; ++a)
-#pragma unroll
-        for (int b = 0; b < 4; ++b) sc[a][b] = 0.f;
     for (int kk = 0; kk < D; kk += 16) {
         uint32_t a[4];
         const __nv_bfloat16* qp = Qs + (r0 + g) * QS + kk + 2 * tq;
@@ -538,12 +531,13 @@ __device__ __forceinline__ void lt_out_warp(const __nv_bfloat16* __restrict__ Qs
             const int t = r0 + g + (i >> 1) * 8, j = nt * 8 + 2 * tq + (i & 1);
             sc[nt][i] = j <= t ? sc[nt][i] * pw[t - j] : 0.f;
         }
-    // ---- what the state before the chunk gives: p[t + 1] S0^T q_t
-    float acc[8][4];
-#pragma unroll
-    for (int a = 0; a < 8; ++a)
-#pragma unroll
-        for (int b = 0; b < 4; ++b) acc[a][b] = 0.f;
+}
+// What the state before the chunk gives: p[t + 1] S0^T q_t.
+template <bool FULL>
+__device__ __forceinline__ void lt_out_inter(const __nv_bfloat16* __restrict__ Qs, const __nv_bfloat16* __restrict__ Shi,
+                                             const __nv_bfloat16* __restrict__ Slo, const float* __restrict__ pw, int QS, int VS,
+                                             int D, int r0, int vh, int pairs, float (&acc)[8][4]) {
+    const int lane = threadIdx.x & 31, g = lane >> 2, tq = lane & 3, blk = lane >> 3, rr = lane & 7;
     for (int kk = 0; kk < D; kk += 16) {
         uint32_t a[4];
         const __nv_bfloat16* qp = Qs + (r0 + g) * QS + kk + 2 * tq;
@@ -565,17 +559,21 @@ __device__ __forceinline__ void lt_out_warp(const __nv_bfloat16* __restrict__ Qs
             }
         }
     }
-    {
-        const float p_lo = pw[min(r0 + g + 1, LT_C)], p_hi = pw[min(r0 + g + 9, LT_C)];
+    const float p_lo = pw[min(r0 + g + 1, LT_C)], p_hi = pw[min(r0 + g + 9, LT_C)];
 #pragma unroll
-        for (int nt = 0; nt < 8; ++nt) {
-            acc[nt][0] *= p_lo;
-            acc[nt][1] *= p_lo;
-            acc[nt][2] *= p_hi;
-            acc[nt][3] *= p_hi;
-        }
+    for (int nt = 0; nt < 8; ++nt) {
+        acc[nt][0] *= p_lo;
+        acc[nt][1] *= p_lo;
+        acc[nt][2] *= p_hi;
+        acc[nt][3] *= p_hi;
     }
-    // ---- what the chunk's own tokens give: sum_(j <= t) A[t, j] v_j
+}
+// What the chunk's own tokens give, sum_(j <= t) A[t, j] v_j, added; then the warp's rows of the output.
+template <int MW, bool FULL>
+__device__ __forceinline__ void lt_out_intra(const float (&sc)[8][4], const __nv_bfloat16* __restrict__ Vs, int VS, int vh, int pairs,
+                                             int n, float (&acc)[8][4], float* __restrict__ out, size_t out_stride) {
+    const int lane = threadIdx.x & 31, g = lane >> 2, tq = lane & 3, blk = lane >> 3, rr = lane & 7;
+    constexpr int r0 = MW * 16;
 #pragma unroll
     for (int kt = 0; kt < 4; ++kt) {
         if (kt <= MW) {
@@ -609,12 +607,14 @@ __device__ __forceinline__ void lt_out_warp(const __nv_bfloat16* __restrict__ Qs
 }
 
 // grid (chunks of the longest request x column tiles of VT, H, requests); VT 64 or 128; VT / 64 groups of four warps,
-// a group owns 64 columns, a warp of it 16 tokens of the chunk (the groups compute the same scores).
+// a group owns 64 columns, a warp of it 16 tokens of the chunk (the groups compute the same scores).  The values are
+// copied after the scores, into the keys' place when they fit there (D >= VT: `v_in_k`), while the warps multiply with
+// the state before the chunk; that leaves room for two blocks on an SM at 128 x 128 heads.
 template <int VT>
-__global__ void __launch_bounds__(VT * 2)
+__global__ void __launch_bounds__(VT * 2, VT == 128 ? 2 : 3)
 lightning_chunk_out_tc_kernel(const __nv_bfloat16* __restrict__ proj, int ld, const int* __restrict__ cu_q,
                               const float* __restrict__ decay, const float* __restrict__ buf, float* __restrict__ out,
-                              int H, int D, int V, int v_tiles) {
+                              int H, int D, int V, int v_tiles, int v_in_k) {
     extern __shared__ __align__(16) unsigned char lt_raw[];
     __shared__ float pw[LT_C + 1];
     __shared__ int base_s;
@@ -622,9 +622,9 @@ lightning_chunk_out_tc_kernel(const __nv_bfloat16* __restrict__ proj, int ld, co
     const int QS = D + 8;
     __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(lt_raw);       // [LT_C][QS]
     __nv_bfloat16* Ks = Qs + LT_C * QS;                                 // [LT_C][QS]
-    __nv_bfloat16* Vs = Ks + LT_C * QS;                                 // [LT_C][VS]
-    __nv_bfloat16* Shi = Vs + LT_C * VS;                                // [D][VS] the state before the chunk
+    __nv_bfloat16* Shi = Ks + LT_C * QS;                                // [D][VS] the state before the chunk
     __nv_bfloat16* Slo = Shi + D * VS;
+    __nv_bfloat16* Vs = v_in_k ? Ks : Slo + D * VS;                     // [LT_C][VS]
     const int tid = threadIdx.x, warp = tid >> 5;
     const int head = blockIdx.y, seq = blockIdx.z;
     const int chunk = blockIdx.x / v_tiles, v0 = (blockIdx.x % v_tiles) * VT;
@@ -643,31 +643,51 @@ lightning_chunk_out_tc_kernel(const __nv_bfloat16* __restrict__ proj, int ld, co
     const __nv_bfloat16* row0 = proj + (size_t)c0 * ld;
     lt_copy_raw<LT_OUT_TC_THREADS>(row0 + (size_t)head * D, ld, n, LT_C, D, D, Qs, QS);
     lt_copy_raw<LT_OUT_TC_THREADS>(row0 + (size_t)(H + head) * D, ld, n, LT_C, D, D, Ks, QS);
-    lt_copy_raw<LT_OUT_TC_THREADS>(row0 + (size_t)2 * H * D + (size_t)head * V + v0, ld, n, LT_C, vt, VT, Vs, VS);
     lt_cp_async_commit();
     lt_copy_raw<LT_OUT_TC_THREADS>(S0, V, D, D, vt, VT, Shi, VS);                  // the two planes of the state before
     lt_copy_raw<LT_OUT_TC_THREADS>(S0 + (size_t)D * V, V, D, D, vt, VT, Slo, VS);
     lt_cp_async_commit();
-    lt_cp_async_wait<1>();                                 // q, k, v are here; the state's planes are still under way
+    lt_cp_async_wait<1>();                                 // q and k are here; the state's planes are still under way
     lt_activate_own<LT_OUT_TC_THREADS>(n, D, D, Qs, nullptr, QS, nullptr, 0);
     lt_activate_own<LT_OUT_TC_THREADS>(n, D, D, Ks, nullptr, QS, nullptr, 0);
-    lt_activate_own<LT_OUT_TC_THREADS>(n, vt, VT, Vs, nullptr, VS, nullptr, 0);
-    lt_cp_async_wait<0>();
     __syncthreads();
     const int mw = warp & 3, vh = (warp >> 2) * 64;       // the warp's tokens and its columns of the tile
-    if (mw * 16 >= n || vh >= vt) return;
-    const int pairs = min(4, (vt - vh) / 16);
+    const bool active = mw * 16 < n && vh < vt;           // the others only copy and wait with the block
+    const int pairs = min(4, max(0, vt - vh) / 16);
+    float sc[8][4], acc[8][4];
+#pragma unroll
+    for (int a = 0; a < 8; ++a)
+#pragma unroll
+        for (int b = 0; b < 4; ++b) sc[a][b] = acc[a][b] = 0.f;
+    if (active) {
+        if (mw == 0) lt_out_scores<0>(Qs, Ks, pw, QS, D, sc);
+        else if (mw == 1) lt_out_scores<1>(Qs, Ks, pw, QS, D, sc);
+        else if (mw == 2) lt_out_scores<2>(Qs, Ks, pw, QS, D, sc);
+        else lt_out_scores<3>(Qs, Ks, pw, QS, D, sc);
+    }
+    lt_cp_async_wait<0>();
+    __syncthreads();                                      // the state's planes are here; nobody reads the keys any more
+    lt_copy_raw<LT_OUT_TC_THREADS>(row0 + (size_t)2 * H * D + (size_t)head * V + v0, ld, n, LT_C, vt, VT, Vs, VS);
+    lt_cp_async_commit();
+    if (active) {
+        if (pairs == 4) lt_out_inter<true>(Qs, Shi, Slo, pw, QS, VS, D, mw * 16, vh, pairs, acc);
+        else lt_out_inter<false>(Qs, Shi, Slo, pw, QS, VS, D, mw * 16, vh, pairs, acc);
+    }
+    lt_cp_async_wait<0>();
+    lt_activate_own<LT_OUT_TC_THREADS>(n, vt, VT, Vs, nullptr, VS, nullptr, 0);
+    __syncthreads();
+    if (!active) return;
     float* o = out + (size_t)c0 * H * V + (size_t)head * V + v0;
-#define LT_OUT_WARP(MW)                                                                                                  \
-    do {                                                                                                                 \
-        if (pairs == 4) lt_out_warp<MW, true>(Qs, Ks, Vs, Shi, Slo, pw, QS, VS, D, vh, pairs, n, o, (size_t)H * V);      \
-        else lt_out_warp<MW, false>(Qs, Ks, Vs, Shi, Slo, pw, QS, VS, D, vh, pairs, n, o, (size_t)H * V);                \
+#define LT_OUT_INTRA(MW)                                                                                   \
+    do {                                                                                                   \
+        if (pairs == 4) lt_out_intra<MW, true>(sc, Vs, VS, vh, pairs, n, acc, o, (size_t)H * V);           \
+        else lt_out_intra<MW, false>(sc, Vs, VS, vh, pairs, n, acc, o, (size_t)H * V);                     \
     } while (0)
-    if (mw == 0) LT_OUT_WARP(0);
-    else if (mw == 1) LT_OUT_WARP(1);
-    else if (mw == 2) LT_OUT_WARP(2);
-    else LT_OUT_WARP(3);
-#undef LT_OUT_WARP
+    if (mw == 0) LT_OUT_INTRA(0);
+    else if (mw == 1) LT_OUT_INTRA(1);
+    else if (mw == 2) LT_OUT_INTRA(2);
+    else LT_OUT_INTRA(3);
+#undef LT_OUT_INTRA
 }
 
 // A step of single tokens: S <- decay S + k v^T, o = S^T q; every state is read and written once.
@@ -862,9 +882,13 @@ NI_EXPORT int ni_lightning_recurrence(const void* proj, int dtype, int ld, float
                     (reinterpret_cast<size_t>(out) & 7) == 0;
     if (tc) {
         const size_t smem_kv = ((size_t)2 * LT_C * (D + 8) + (size_t)LT_C * (V + 8)) * sizeof(__nv_bfloat16);
-        const size_t smem_wide = ((size_t)2 * LT_C * (D + 8) + (size_t)LT_C * (128 + 8) + (size_t)2 * D * (128 + 8)) * sizeof(__nv_bfloat16);
-        const int VT = V > 64 && smem_wide <= 160 * 1024 ? 128 : 64;
-        const size_t smem_out = ((size_t)2 * LT_C * (D + 8) + (size_t)LT_C * (VT + 8) + (size_t)2 * D * (VT + 8)) * sizeof(__nv_bfloat16);
+        // shared memory of the read-out kernel: q, k, the two planes of the state, and the values unless they take the keys' place
+        auto out_bytes = [&](int vt) {
+            return ((size_t)2 * LT_C * (D + 8) + (size_t)2 * D * (vt + 8) + (D >= vt ? 0 : (size_t)LT_C * (vt + 8))) * sizeof(__nv_bfloat16);
+        };
+        const int VT = V > 64 && out_bytes(128) <= 160 * 1024 ? 128 : 64;
+        const int v_in_k = D >= VT;
+        const size_t smem_out = out_bytes(VT);
         if (smem_kv <= 200 * 1024 && smem_out <= 200 * 1024) {
             const int vt_tiles = (V + VT - 1) / VT;
             const __nv_bfloat16* p = (const __nv_bfloat16*)proj;
@@ -874,11 +898,11 @@ NI_EXPORT int ni_lightning_recurrence(const void* proj, int dtype, int ld, float
             if (VT == 128) {
                 cudaFuncSetAttribute(lightning_chunk_out_tc_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_out);
                 lightning_chunk_out_tc_kernel<128><<<dim3(per_seq * vt_tiles, H, n_seqs), 256, smem_out, stream>>>(
-                    p, ld, cu_q, decay, before, out, H, D, V, vt_tiles);
+                    p, ld, cu_q, decay, before, out, H, D, V, vt_tiles, v_in_k);
             } else {
                 cudaFuncSetAttribute(lightning_chunk_out_tc_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_out);
                 lightning_chunk_out_tc_kernel<64><<<dim3(per_seq * vt_tiles, H, n_seqs), 128, smem_out, stream>>>(
-                    p, ld, cu_q, decay, before, out, H, D, V, vt_tiles);
+                    p, ld, cu_q, decay, before, out, H, D, V, vt_tiles, v_in_k);
             }
             NI_RETURN_LAUNCH_STATUS();
         }
