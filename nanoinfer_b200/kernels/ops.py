@@ -601,8 +601,9 @@ LIGHTNING_MAX_DIM = 256      # the largest key size whose chunk buffers fit a bl
 
 
 def lightning_max_chunks(n_tokens: int, n_seqs: int) -> int:
-    """The most chunks that ``n_seqs`` requests with ``n_tokens`` tokens in all are cut into (the size of
-    lightning_recurrence's buffer, in units of H dim vdim floats)."""
+    """The size of lightning_recurrence's buffer in units of H dim vdim floats, for ``n_seqs`` requests with
+    ``n_tokens`` tokens in all: two entries (its own sum, the state before it) for each of the most chunks they
+    can be cut into."""
     return int(load("lightning").ni_lightning_max_chunks(int(n_tokens), int(n_seqs)))
 
 
