@@ -502,13 +502,13 @@ lightning_chunk_kv_tc_kernel(const __nv_bfloat16* __restrict__ proj, int ld, con
 }
 
 // The three phases of one warp of lightning_chunk_out_tc_kernel: tokens MW * 16 .. MW * 16 + 15 of the chunk, columns
-// vh .. vh + 16 pairs - 1 of the block's tile (FULL: all 64, no checks inside the loops).
+// vh .. vh + 16 pairs - 1 of the block's tile (FULL: all 64, no column checks inside the loops).  One instance of the
+// loops serves all warps: tiles beyond a warp's diagonal are skipped by a branch that the whole warp takes alike.
 // Scores of the warp's 16 tokens with the keys up to their diagonal block, decayed and masked.
-template <int MW>
 __device__ __forceinline__ void lt_out_scores(const __nv_bfloat16* __restrict__ Qs, const __nv_bfloat16* __restrict__ Ks,
-                                              const float* __restrict__ pw, int QS, int D, float (&sc)[8][4]) {
+                                              const float* __restrict__ pw, int QS, int D, int MW, float (&sc)[8][4]) {
     const int lane = threadIdx.x & 31, g = lane >> 2, tq = lane & 3;
-    constexpr int r0 = MW * 16;
+    const int r0 = MW * 16;
     for (int kk = 0; kk < D; kk += 16) {
         uint32_t a[4];
         const __nv_bfloat16* qp = Qs + (r0 + g) * QS + kk + 2 * tq;
@@ -569,11 +569,11 @@ __device__ __forceinline__ void lt_out_inter(const __nv_bfloat16* __restrict__ Q
     }
 }
 // What the chunk's own tokens give, sum_(j <= t) A[t, j] v_j, added; then the warp's rows of the output.
-template <int MW, bool FULL>
+template <bool FULL>
 __device__ __forceinline__ void lt_out_intra(const float (&sc)[8][4], const __nv_bfloat16* __restrict__ Vs, int VS, int vh, int pairs,
-                                             int n, float (&acc)[8][4], float* __restrict__ out, size_t out_stride) {
+                                             int n, int MW, float (&acc)[8][4], float* __restrict__ out, size_t out_stride) {
     const int lane = threadIdx.x & 31, g = lane >> 2, tq = lane & 3, blk = lane >> 3, rr = lane & 7;
-    constexpr int r0 = MW * 16;
+    const int r0 = MW * 16;
 #pragma unroll
     for (int kt = 0; kt < 4; ++kt) {
         if (kt <= MW) {
@@ -659,12 +659,7 @@ lightning_chunk_out_tc_kernel(const __nv_bfloat16* __restrict__ proj, int ld, co
     for (int a = 0; a < 8; ++a)
 #pragma unroll
         for (int b = 0; b < 4; ++b) sc[a][b] = acc[a][b] = 0.f;
-    if (active) {
-        if (mw == 0) lt_out_scores<0>(Qs, Ks, pw, QS, D, sc);
-        else if (mw == 1) lt_out_scores<1>(Qs, Ks, pw, QS, D, sc);
-        else if (mw == 2) lt_out_scores<2>(Qs, Ks, pw, QS, D, sc);
-        else lt_out_scores<3>(Qs, Ks, pw, QS, D, sc);
-    }
+    if (active) lt_out_scores(Qs, Ks, pw, QS, D, mw, sc);
     lt_cp_async_wait<0>();
     __syncthreads();                                      // the state's planes are here; nobody reads the keys any more
     lt_copy_raw<LT_OUT_TC_THREADS>(row0 + (size_t)2 * H * D + (size_t)head * V + v0, ld, n, LT_C, vt, VT, Vs, VS);
@@ -678,16 +673,8 @@ lightning_chunk_out_tc_kernel(const __nv_bfloat16* __restrict__ proj, int ld, co
     __syncthreads();
     if (!active) return;
     float* o = out + (size_t)c0 * H * V + (size_t)head * V + v0;
-#define LT_OUT_INTRA(MW)                                                                                   \
-    do {                                                                                                   \
-        if (pairs == 4) lt_out_intra<MW, true>(sc, Vs, VS, vh, pairs, n, acc, o, (size_t)H * V);           \
-        else lt_out_intra<MW, false>(sc, Vs, VS, vh, pairs, n, acc, o, (size_t)H * V);                     \
-    } while (0)
-    if (mw == 0) LT_OUT_INTRA(0);
-    else if (mw == 1) LT_OUT_INTRA(1);
-    else if (mw == 2) LT_OUT_INTRA(2);
-    else LT_OUT_INTRA(3);
-#undef LT_OUT_INTRA
+    if (pairs == 4) lt_out_intra<true>(sc, Vs, VS, vh, pairs, n, mw, acc, o, (size_t)H * V);
+    else lt_out_intra<false>(sc, Vs, VS, vh, pairs, n, mw, acc, o, (size_t)H * V);
 }
 
 // A step of single tokens: S <- decay S + k v^T, o = S^T q; every state is read and written once.
