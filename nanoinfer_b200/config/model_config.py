@@ -28,7 +28,8 @@ class RopeScaling:
     """Frequency rescaling rule of a rotary position encoding.
 
     ``rope_type == "llama3"`` is the piecewise rule of
-    src/op/kernels/cpu/rope_kernel.cpp:117-139.  ``rope_type == "yarn"`` is a ramp over the frequencies (position
+    src/op/kernels/cpu/rope_kernel.cpp:117-139.  ``rope_type == "linear"`` divides every frequency by ``factor`` (the
+    other fields are not read).  ``rope_type == "yarn"`` is a ramp over the frequencies (position
     kind "rope_yarn"), whose two turn counts ``fast`` and ``slow`` travel as high_freq_factor and low_freq_factor.
     """
     rope_type: str
@@ -46,7 +47,8 @@ class PositionSpec:
     what projection weights stored in the safetensors layout expect; "interleaved"
     rotates (2i, 2i+1), the reference kernels' convention
     (src/op/kernels/cpu/rope_kernel.cpp:68-93) for weights permuted by its exporter.
-    kind "none": no encoding.
+    kind "rope_scaled": rotary with frequencies computed in double precision and the rescaling rule "linear" or
+    "llama3" of ``scaling``.  kind "none": no encoding.
     """
     kind: str = "rope"
     theta: float = 10000.0
@@ -134,8 +136,13 @@ class LayerSpec:
     arrangement "sandwich_norm":  h += post1(mixer(norm1(h))); h += post2(ffn(norm2(h))) - every sublayer's
     output passes a norm of its own (``mixer_post_norm``, ``ffn_post_norm``) before it joins the stream;
     the feed-forward with its two norms may be absent.
+    arrangement "output_norm":  h += norm1(mixer(h)); h += norm2(ffn(h)) - the sublayers read the stream itself and
+    ``mixer_norm`` / ``ffn_norm`` are the norms on their OUTPUTS.
     ``extra`` carries the arrangement's own constants (for instance the width of a per-layer token
     input that it adds after the feed-forward).
+
+    A layer that no run of the schedule names has no tensors and is not built (an entry that only repeats
+    another layer's sizes because it runs with that layer's weights).
     """
     mixer: MixerSpec
     feed_forward: Optional[FeedForwardSpec]

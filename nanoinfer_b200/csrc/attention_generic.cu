@@ -9,6 +9,9 @@
 // the bias and the softmax.
 // Values may have a size of their own (v_dim): the value pages are then [P, Hkv, page, v_dim] and the output
 // [T, Hq, v_dim].
+// Two more masks and one more denominator, all parameters: `chunk` > 0 lets a token see only the keys of its own
+// chunk, [p - p % chunk, p], chunks counted from the sequence's position 0; `sink` adds one to the softmax's
+// denominator - a key of score 0 without a value - so the weights of a token sum to less than one.
 //
 // The result of a token depends only on its own keys and their order, never on how the
 // step was cut or what else is in the batch, so this kernel is the FP32 path's attention
@@ -31,7 +34,8 @@ __global__ void attention_generic_kernel(const T* __restrict__ q, const T* __res
                                          const int* __restrict__ block_table, int bt_stride,
                                          int n_tokens, int n_q_heads, int n_kv_heads, int head_dim,
                                          int page_size, int window, float scale,
-                                         const float* __restrict__ head_slopes, float score_cap, int v_dim) {
+                                         const float* __restrict__ head_slopes, float score_cap, int v_dim, int chunk,
+                                         int sink) {
     const int warps_per_block = blockDim.x >> 5;
     const long long item = (long long)blockIdx.x * warps_per_block + (threadIdx.x >> 5);
     if (item >= (long long)n_tokens * n_q_heads) return;
@@ -42,7 +46,8 @@ __global__ void attention_generic_kernel(const T* __restrict__ q, const T* __res
     const int kvh = head / (n_q_heads / n_kv_heads);
     const int pos = positions[t];
     const int* table = block_table + (size_t)seq_of_token[t] * bt_stride;
-    const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+    int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+    if (chunk > 0 && pos - pos % chunk > lo) lo = pos - pos % chunk;
     const float slope = head_slopes ? head_slopes[head] : 0.f;
 
     float qr[ATT_MAX_REGS], acc[ATT_MAX_REGS];
@@ -53,7 +58,7 @@ __global__ void attention_generic_kernel(const T* __restrict__ q, const T* __res
         qr[r] = dim < head_dim ? ni_to_float(qrow[dim]) : 0.f;
         acc[r] = 0.f;
     }
-    float m = -INFINITY, l = 0.f;
+    float m = sink ? 0.f : -INFINITY, l = sink ? 1.f : 0.f;      // the sink: a key of score 0 that is there from the start
     for (int j = lo; j <= pos; ++j) {
         const int page = table[j / page_size];
         const size_t slot = ((size_t)page * n_kv_heads + kvh) * page_size + (j % page_size);
@@ -94,9 +99,9 @@ NI_EXPORT int ni_attention_generic(const void* q, int dtype, const void* k_pages
                                    const int* positions, const int* seq_of_token, const int* block_table, int bt_stride,
                                    int n_tokens, int n_q_heads, int n_kv_heads, int head_dim,
                                    int page_size, int window, float scale, const float* head_slopes,
-                                   float score_cap, int v_dim, cudaStream_t stream) {
+                                   float score_cap, int v_dim, int chunk, int sink, cudaStream_t stream) {
     if (n_tokens <= 0) return NI_OK;
-    if (n_q_heads <= 0 || n_kv_heads <= 0 || n_q_heads % n_kv_heads || head_dim <= 0 || page_size <= 0 || v_dim < 0)
+    if (n_q_heads <= 0 || n_kv_heads <= 0 || n_q_heads % n_kv_heads || head_dim <= 0 || page_size <= 0 || v_dim < 0 || chunk < 0)
         return NI_ERR_BAD_ARGUMENT;
     if (v_dim == 0) v_dim = head_dim;          // values of the keys' size
     if (head_dim > 32 * 16 || v_dim > 32 * 16) return NI_ERR_UNSUPPORTED_SIZE;
@@ -108,7 +113,7 @@ NI_EXPORT int ni_attention_generic(const void* q, int dtype, const void* k_pages
     attention_generic_kernel<T, R><<<(int)blocks, warps * 32, 0, stream>>>(                         \
         (const T*)q, (const T*)k_pages, (const T*)v_pages, (T*)out, token_list, positions,         \
         seq_of_token,                                                                               \
-        block_table, bt_stride, n_tokens, n_q_heads, n_kv_heads, head_dim, page_size, window, scale, head_slopes, score_cap, v_dim)
+        block_table, bt_stride, n_tokens, n_q_heads, n_kv_heads, head_dim, page_size, window, scale, head_slopes, score_cap, v_dim, chunk, sink)
 #define LAUNCH(T)                          \
     do {                                   \
         if (head_dim <= 256 && v_dim <= 256) LAUNCH_R(T, 8); \

@@ -100,3 +100,78 @@ NI_EXPORT int ni_head_gate(void* x, int dtype, const void* proj, int ld, int col
         return NI_ERR_BAD_ARGUMENT;
     NI_RETURN_LAUNCH_STATUS();
 }
+
+
+// A latent cache row with a rotated key part: beside c = RMSNorm(first R columns) * weight a token keeps rot_dim more
+// numbers - one key part that all heads share and that is rotated by position - so a page row is [c | rot(k_r)], R +
+// rot_dim wide.  The same launch rotates the last rot_dim dimensions of every head of q [T, H (R + rot_dim)] in place
+// (queries that were carried into the latent space, with their rotated part behind).  Rotation: the angle
+// float(position) * inv_freq[i] turns the pair (2i, 2i + 1) (`interleaved`) or (i, i + rot_dim / 2).
+// One block per token.
+template <typename T>
+__global__ void latent_rope_write_kernel(const T* __restrict__ proj, int ld, int col0, const float* __restrict__ weight,
+                                         float eps, T* __restrict__ pages, const int* __restrict__ positions,
+                                         const int* __restrict__ seq_of_token, const int* __restrict__ block_table,
+                                         int bt_stride, int R, int rot_dim, int page_size, const float* __restrict__ inv_freq,
+                                         int interleaved, T* __restrict__ q, int H) {
+    __shared__ float scratch[32];
+    extern __shared__ __align__(16) float cs[];          // [rot_dim]: cosines, then sines
+    const int t = blockIdx.x, half = rot_dim >> 1, W = R + rot_dim;
+    const int pos = positions[t];
+    for (int i = threadIdx.x; i < half; i += blockDim.x) {
+        float s, c;
+        sincosf((float)pos * inv_freq[i], &s, &c);
+        cs[i] = c;
+        cs[half + i] = s;
+    }
+    const T* x = proj + (size_t)t * ld + col0;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < R; i += blockDim.x) {
+        const float v = ni_to_float(x[i]);
+        ss += v * v;
+    }
+    ss = ni_block_sum(ss, scratch);                      // (its barriers also publish cs)
+    const float inv = 1.0f / sqrtf(ss / (float)R + eps);
+    if (pages) {
+        const int page = block_table[(size_t)seq_of_token[t] * bt_stride + pos / page_size];
+        T* dst = pages + ((size_t)page * page_size + pos % page_size) * W;
+        for (int i = threadIdx.x; i < R; i += blockDim.x) dst[i] = ni_from_float<T>(ni_to_float(x[i]) * inv * weight[i]);
+        for (int i = threadIdx.x; i < half; i += blockDim.x) {
+            const int a = interleaved ? 2 * i : i, b = interleaved ? 2 * i + 1 : i + half;
+            const float u = ni_to_float(x[R + a]), v = ni_to_float(x[R + b]);
+            dst[R + a] = ni_from_float<T>(u * cs[i] - v * cs[half + i]);
+            dst[R + b] = ni_from_float<T>(v * cs[i] + u * cs[half + i]);
+        }
+    }
+    for (int j = threadIdx.x; j < H * half; j += blockDim.x) {
+        const int head = j / half, i = j - head * half;
+        const int a = interleaved ? 2 * i : i, b = interleaved ? 2 * i + 1 : i + half;
+        T* qr = q + ((size_t)t * H + head) * W + R;
+        const float u = ni_to_float(qr[a]), v = ni_to_float(qr[b]);
+        qr[a] = ni_from_float<T>(u * cs[i] - v * cs[half + i]);
+        qr[b] = ni_from_float<T>(v * cs[i] + u * cs[half + i]);
+    }
+}
+
+// proj columns [col0, col0 + R + rot_dim): the latent, then the shared key part; pages [P, page_size, R + rot_dim] (null:
+// nothing is written); q [T, H (R + rot_dim)].
+NI_EXPORT int ni_latent_rope_write(const void* proj, int dtype, int ld, int col0, const float* weight, float eps,
+                                   void* pages, const int* positions, const int* seq_of_token, const int* block_table,
+                                   int bt_stride, int n_tokens, int R, int rot_dim, int page_size, const float* inv_freq,
+                                   int interleaved, void* q, int H, cudaStream_t stream) {
+    if (n_tokens <= 0) return NI_OK;
+    if (R <= 0 || rot_dim < 0 || (rot_dim & 1) || page_size <= 0 || col0 < 0 || col0 + R + rot_dim > ld || H <= 0)
+        return NI_ERR_BAD_ARGUMENT;
+    const size_t smem = (size_t)(rot_dim > 0 ? rot_dim : 1) * sizeof(float);
+    if (smem > 48 * 1024) return NI_ERR_UNSUPPORTED_SIZE;
+    const int threads = R >= 1024 ? 256 : 128;
+#define LAUNCH(T)                                                                                                     \
+    latent_rope_write_kernel<T><<<n_tokens, threads, smem, stream>>>((const T*)proj, ld, col0, weight, eps, (T*)pages, \
+                                                                     positions, seq_of_token, block_table, bt_stride, R, \
+                                                                     rot_dim, page_size, inv_freq, interleaved, (T*)q, H)
+    if (dtype == NI_DTYPE_F32) LAUNCH(float);
+    else if (dtype == NI_DTYPE_BF16) LAUNCH(__nv_bfloat16);
+    else return NI_ERR_BAD_ARGUMENT;
+#undef LAUNCH
+    NI_RETURN_LAUNCH_STATUS();
+}

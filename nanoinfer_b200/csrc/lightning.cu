@@ -42,6 +42,13 @@ template <> __device__ __forceinline__ float lt_act<__nv_bfloat16>(__nv_bfloat16
     return __bfloat162float(__float2bfloat16_rn(__fdividef(z, 1.0f + __expf(-z))));
 }
 
+// An FP32 entry that enters the recurrence as it is (no activation): the caller has made q, k and v itself, for
+// instance rotated queries and scaled keys of a retention layer.  A type of its own, so that the FP32 FMA kernels
+// below get a second instance and the ones with silu stay as they are.
+struct LtPlain { float v; };
+template <> __device__ __forceinline__ float ni_to_float<LtPlain>(LtPlain x) { return x.v; }
+template <> __device__ __forceinline__ float lt_act<LtPlain>(LtPlain raw) { return raw.v; }
+
 // dst[r * dst_stride + c] = f(src[r * ld + c]) * scale[r] for r < rows, c < cols (zero for rows .. rows_pad - 1 and
 // c in cols .. cols_pad - 1).  16 bytes per load when every row starts on 16 bytes and cols is a multiple of the
 // vector's elements.
@@ -833,21 +840,27 @@ NI_EXPORT int ni_lightning_max_chunks(int n_tokens, int n_seqs) { return (int)(2
 // proj [T, ld] with columns q (H D) | k (H D) | v (H V) | ...; state FP32 [slots, state_stride] holding S [H, D, V] of
 // every request; decay FP32 [H]; out FP32 [T, H V].  The state advances by the step's tokens.  max_q_len: the most
 // tokens that one request brings (1: a step of single tokens, which needs no buffer); buf FP32 with room for
-// buf_chunks x H D V, at least ni_lightning_max_chunks(n_tokens, n_seqs) of them.
+// buf_chunks x H D V, at least ni_lightning_max_chunks(n_tokens, n_seqs) of them.  activation 1: q, k, v = silu of
+// proj's entries; 0: proj (FP32 only) holds q, k and v themselves.
 NI_EXPORT int ni_lightning_recurrence(const void* proj, int dtype, int ld, float* state, long long state_stride,
                                       const int* cu_q, const int* slots, const float* decay, float* out, int n_tokens,
                                       int n_seqs, int max_q_len, float* buf, long long buf_chunks, int H, int D, int V,
-                                      cudaStream_t stream) {
+                                      int activation, cudaStream_t stream) {
     if (n_tokens <= 0 || n_seqs <= 0) return NI_OK;
     if (H <= 0 || D <= 0 || V <= 0 || ld < 2 * H * D + H * V || state_stride < (long long)H * D * V || max_q_len <= 0)
         return NI_ERR_BAD_ARGUMENT;
     if (dtype != NI_DTYPE_F32 && dtype != NI_DTYPE_BF16) return NI_ERR_BAD_ARGUMENT;
+    if (activation != 0 && activation != 1) return NI_ERR_BAD_ARGUMENT;
+    if (activation == 0 && dtype != NI_DTYPE_F32) return NI_ERR_BAD_ARGUMENT;
     if (H > 65535 || n_seqs > 65535) return NI_ERR_UNSUPPORTED_SIZE;
     if (max_q_len == 1) {
         dim3 grid((V + 127) / 128, H, n_seqs);
         const size_t smem = ((size_t)2 * D + (LT_THREADS / 32) * 128) * sizeof(float);
         if (smem > 48 * 1024) return NI_ERR_UNSUPPORTED_SIZE;
-        if (dtype == NI_DTYPE_F32)
+        if (activation == 0)
+            lightning_token_kernel<LtPlain><<<grid, LT_THREADS, smem, stream>>>((const LtPlain*)proj, ld, state, state_stride,
+                                                                                 cu_q, slots, decay, out, H, D, V);
+        else if (dtype == NI_DTYPE_F32)
             lightning_token_kernel<float><<<grid, LT_THREADS, smem, stream>>>((const float*)proj, ld, state, state_stride, cu_q,
                                                                                slots, decay, out, H, D, V);
         else
@@ -909,7 +922,8 @@ NI_EXPORT int ni_lightning_recurrence(const void* proj, int dtype, int ld, float
                                                                                       out, H, D, V, v_tiles);            \
         }                                                                                                                \
     } while (0)
-    if (dtype == NI_DTYPE_F32) LAUNCH(float);
+    if (activation == 0) LAUNCH(LtPlain);
+    else if (dtype == NI_DTYPE_F32) LAUNCH(float);
     else LAUNCH(__nv_bfloat16);
 #undef LAUNCH
     NI_RETURN_LAUNCH_STATUS();
@@ -932,5 +946,108 @@ NI_EXPORT int ni_lightning_gated_norm(const float* o, const void* proj, int dtyp
     else if (dtype == NI_DTYPE_BF16) LAUNCH(__nv_bfloat16);
     else return NI_ERR_BAD_ARGUMENT;
 #undef LAUNCH
+    NI_RETURN_LAUNCH_STATUS();
+}
+
+
+// ---- what a retention layer puts around the recurrence ------------------------------------------------------------
+//
+// Retention is the same recurrence with other things before and after it: queries and keys are rotated by position
+// (the first rotary_dim dimensions of every head, dimension i paired with i + rotary_dim / 2, angle = float(position)
+// * inv_freq[i]), keys are then multiplied by k_scale, nothing is activated; every head's read-out is divided by its
+// own root mean square and multiplied by an activation of a gate projection.
+
+// qkv[t] = [rot(q) | rot(k) * k_scale | v] as FP32, from proj [T, ld] with columns q (H D) | k (H D) | v (H V) | ...
+template <typename T>
+__global__ void __launch_bounds__(256)
+linear_attention_prepare_kernel(const T* __restrict__ proj, int ld, const int* __restrict__ positions,
+                                const float* __restrict__ inv_freq, float k_scale, float* __restrict__ qkv, int H, int D, int V,
+                                int rotary_dim) {
+    extern __shared__ __align__(16) float cs[];          // [rotary_dim]: cosines, then sines
+    const int t = blockIdx.x, half = rotary_dim >> 1, nqk = 2 * H * D, nv = H * V;
+    const float pos = (float)positions[t];
+    for (int i = threadIdx.x; i < half; i += blockDim.x) {
+        float s, c;
+        sincosf(pos * inv_freq[i], &s, &c);
+        cs[i] = c;
+        cs[half + i] = s;
+    }
+    __syncthreads();
+    const T* x = proj + (size_t)t * ld;
+    float* o = qkv + (size_t)t * (nqk + nv);
+    for (int i = threadIdx.x; i < nqk; i += blockDim.x) {
+        const int dim = i % D;
+        float a = ni_to_float(x[i]);
+        if (dim < rotary_dim) {
+            const bool first = dim < half;
+            const float b = ni_to_float(x[first ? i + half : i - half]);
+            const int f = first ? dim : dim - half;
+            a = first ? a * cs[f] - b * cs[half + f] : a * cs[f] + b * cs[half + f];
+        }
+        o[i] = i >= H * D ? a * k_scale : a;
+    }
+    for (int i = threadIdx.x; i < nv; i += blockDim.x) o[nqk + i] = ni_to_float(x[nqk + i]);
+}
+
+NI_EXPORT int ni_linear_attention_prepare(const void* proj, int dtype, int ld, const int* positions, const float* inv_freq,
+                                          float k_scale, float* qkv, int n_tokens, int H, int D, int V, int rotary_dim,
+                                          cudaStream_t stream) {
+    if (n_tokens <= 0) return NI_OK;
+    if (H <= 0 || D <= 0 || V <= 0 || rotary_dim < 0 || rotary_dim > D || (rotary_dim & 1) || ld < 2 * H * D + H * V)
+        return NI_ERR_BAD_ARGUMENT;
+    const size_t smem = (size_t)(rotary_dim > 0 ? rotary_dim : 1) * sizeof(float);
+    if (smem > 48 * 1024) return NI_ERR_UNSUPPORTED_SIZE;
+    const int threads = 2 * H * D >= 1024 ? 256 : 128;
+    if (dtype == NI_DTYPE_F32)
+        linear_attention_prepare_kernel<float><<<n_tokens, threads, smem, stream>>>((const float*)proj, ld, positions, inv_freq,
+                                                                                    k_scale, qkv, H, D, V, rotary_dim);
+    else if (dtype == NI_DTYPE_BF16)
+        linear_attention_prepare_kernel<__nv_bfloat16><<<n_tokens, threads, smem, stream>>>(
+            (const __nv_bfloat16*)proj, ld, positions, inv_freq, k_scale, qkv, H, D, V, rotary_dim);
+    else
+        return NI_ERR_BAD_ARGUMENT;
+    NI_RETURN_LAUNCH_STATUS();
+}
+
+// y[t, g, :] = o[t, g, :] / sqrt(mean(o[t, g, :]^2) + eps) * weight[g, :] * act(gate[t, g, :]) for every group g of V
+// neighbouring columns (weight null: 1); the gate's columns lie in proj at col0; gate_act 0: sigmoid, 1: silu.
+// One block per token, a warp takes a group at a time.
+template <typename T>
+__global__ void group_gated_norm_kernel(const float* __restrict__ o, const T* __restrict__ proj, int ld, int col0,
+                                        const float* __restrict__ weight, float eps, T* __restrict__ y, int groups, int V,
+                                        int gate_act) {
+    const int t = blockIdx.x, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
+    const float* row = o + (size_t)t * groups * V;
+    const T* g = proj + (size_t)t * ld + col0;
+    T* yr = y + (size_t)t * groups * V;
+    for (int grp = threadIdx.x >> 5; grp < groups; grp += warps) {
+        const float* x = row + (size_t)grp * V;
+        float ss = 0.f;
+        for (int i = lane; i < V; i += 32) ss = fmaf(x[i], x[i], ss);
+        ss = ni_warp_sum(ss);
+        const float inv = 1.0f / sqrtf(ss / (float)V + eps);
+        for (int i = lane; i < V; i += 32) {
+            const int c = grp * V + i;
+            const float z = ni_to_float(g[c]);
+            const float sig = 1.0f / (1.0f + expf(-z));
+            yr[c] = ni_from_float<T>(x[i] * inv * (weight ? weight[c] : 1.0f) * (gate_act ? z * sig : sig));
+        }
+    }
+}
+
+NI_EXPORT int ni_group_gated_norm(const float* o, const void* proj, int dtype, int ld, int col0, const float* weight,
+                                  float eps, void* y, int n_tokens, int groups, int V, int gate_act, cudaStream_t stream) {
+    if (n_tokens <= 0) return NI_OK;
+    if (groups <= 0 || V <= 0 || col0 < 0 || (long long)col0 + (long long)groups * V > ld || (gate_act != 0 && gate_act != 1))
+        return NI_ERR_BAD_ARGUMENT;
+    const int threads = groups >= 8 ? 256 : (groups >= 4 ? 128 : 64);
+    if (dtype == NI_DTYPE_F32)
+        group_gated_norm_kernel<float><<<n_tokens, threads, 0, stream>>>(o, (const float*)proj, ld, col0, weight, eps, (float*)y,
+                                                                         groups, V, gate_act);
+    else if (dtype == NI_DTYPE_BF16)
+        group_gated_norm_kernel<__nv_bfloat16><<<n_tokens, threads, 0, stream>>>(o, (const __nv_bfloat16*)proj, ld, col0, weight,
+                                                                                 eps, (__nv_bfloat16*)y, groups, V, gate_act);
+    else
+        return NI_ERR_BAD_ARGUMENT;
     NI_RETURN_LAUNCH_STATUS();
 }

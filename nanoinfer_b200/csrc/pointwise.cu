@@ -57,29 +57,30 @@ NI_EXPORT int ni_cast_bf16(const float* x, void* out, long long n, cudaStream_t 
     NI_RETURN_LAUNCH_STATUS();
 }
 
-// h[t, :] += y[t, :] / sqrt(mean(y[t, :]^2) + eps) * weight
+// h[t, :] += z / sqrt(mean(z^2) + eps) * weight with z = y[t, :] (+ bias, FP32 [d], where one is given: a product's
+// bias that its kernel did not add)
 template <typename T>
 __global__ void add_normed_kernel(float* __restrict__ h, const T* __restrict__ y, const float* __restrict__ weight,
-                                  float eps, int d) {
+                                  float eps, int d, const float* __restrict__ bias) {
     __shared__ float scratch[32];
     const int t = blockIdx.x;
     const T* yr = y + (size_t)t * d;
     float* hr = h + (size_t)t * d;
     float ss = 0.f;
     for (int i = threadIdx.x; i < d; i += blockDim.x) {
-        const float v = ni_to_float(yr[i]);
+        const float v = ni_to_float(yr[i]) + (bias ? bias[i] : 0.f);
         ss += v * v;
     }
     ss = ni_block_sum(ss, scratch);
     const float inv = 1.0f / sqrtf(ss / (float)d + eps);
-    for (int i = threadIdx.x; i < d; i += blockDim.x) hr[i] += ni_to_float(yr[i]) * inv * weight[i];
+    for (int i = threadIdx.x; i < d; i += blockDim.x) hr[i] += (ni_to_float(yr[i]) + (bias ? bias[i] : 0.f)) * inv * weight[i];
 }
 
 // The same for FP32 y whose width is a multiple of 4, up to 4,096: the row stays in the block's registers between
 // the sum of squares and the addition, and moves in 16-byte pieces.
 __global__ void __launch_bounds__(256)
 add_normed_f32_vec_kernel(float* __restrict__ h, const float* __restrict__ y, const float* __restrict__ weight, float eps,
-                          int d) {
+                          int d, const float* __restrict__ bias) {
     __shared__ float scratch[32];
     const int t = blockIdx.x;
     const float4* yr = reinterpret_cast<const float4*>(y + (size_t)t * d);
@@ -92,6 +93,10 @@ add_normed_f32_vec_kernel(float* __restrict__ h, const float* __restrict__ y, co
     for (int r = 0; r < 4; ++r) {
         const int i = threadIdx.x + 256 * r;
         v[r] = i < n4 ? yr[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+        if (bias && i < n4) {
+            const float4 b = reinterpret_cast<const float4*>(bias)[i];
+            v[r].x += b.x; v[r].y += b.y; v[r].z += b.z; v[r].w += b.w;
+        }
         ss += v[r].x * v[r].x + v[r].y * v[r].y + v[r].z * v[r].z + v[r].w * v[r].w;
     }
     ss = ni_block_sum(ss, scratch);
@@ -112,16 +117,16 @@ add_normed_f32_vec_kernel(float* __restrict__ h, const float* __restrict__ y, co
 }
 
 NI_EXPORT int ni_add_normed(float* h, const void* y, int y_dtype, const float* weight, float eps, int n_rows, int d,
-                            cudaStream_t stream) {
+                            const float* bias, cudaStream_t stream) {
     if (n_rows <= 0) return NI_OK;
     if (d <= 0) return NI_ERR_BAD_ARGUMENT;
     const int threads = d >= 1024 ? 256 : 128;
-    if (y_dtype == NI_DTYPE_F32 && d % 4 == 0 && d <= 4096 && d >= 512)
-        add_normed_f32_vec_kernel<<<n_rows, 256, 0, stream>>>(h, (const float*)y, weight, eps, d);
+    if (y_dtype == NI_DTYPE_F32 && d % 4 == 0 && d <= 4096 && d >= 512 && (reinterpret_cast<size_t>(bias) & 15) == 0)
+        add_normed_f32_vec_kernel<<<n_rows, 256, 0, stream>>>(h, (const float*)y, weight, eps, d, bias);
     else if (y_dtype == NI_DTYPE_F32)
-        add_normed_kernel<float><<<n_rows, threads, 0, stream>>>(h, (const float*)y, weight, eps, d);
+        add_normed_kernel<float><<<n_rows, threads, 0, stream>>>(h, (const float*)y, weight, eps, d, bias);
     else if (y_dtype == NI_DTYPE_BF16)
-        add_normed_kernel<__nv_bfloat16><<<n_rows, threads, 0, stream>>>(h, (const __nv_bfloat16*)y, weight, eps, d);
+        add_normed_kernel<__nv_bfloat16><<<n_rows, threads, 0, stream>>>(h, (const __nv_bfloat16*)y, weight, eps, d, bias);
     else
         return NI_ERR_BAD_ARGUMENT;
     NI_RETURN_LAUNCH_STATUS();
@@ -290,25 +295,28 @@ NI_EXPORT int ni_scale_f32(float* x, float factor, long long n, cudaStream_t str
 }
 
 // A gated unit with capped arguments: g = min(gate, limit), u = clamp(up, -limit, limit),
-// out = g * sigmoid(slope * g) * (u + shift); gate_up = [gate | up] along the columns.
+// out = g * sigmoid(slope * g) * (u + shift); gate_up = [gate | up] along the columns.  bias (FP32 [2 inter], gate
+// then up, or null) joins gate and up before the limits.
 template <typename T>
 __global__ void capped_glu_kernel(const T* __restrict__ gate_up, T* __restrict__ out, long long n, int inter,
-                                  float limit, float slope, float shift, const float* __restrict__ row_scale) {
+                                  float limit, float slope, float shift, const float* __restrict__ row_scale,
+                                  const float* __restrict__ bias) {
     const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= n) return;
     const long long t = i / inter;
     const int c = (int)(i - t * inter);
     const T* row = gate_up + (size_t)t * 2 * inter;
     const float rs = row_scale ? row_scale[t] : 1.0f;
-    const float g = fminf(ni_to_float(row[c]) * rs, limit);
-    const float u = fminf(fmaxf(ni_to_float(row[inter + c]) * rs, -limit), limit);
+    const float g = fminf(ni_to_float(row[c]) * rs + (bias ? bias[c] : 0.f), limit);
+    const float u = fminf(fmaxf(ni_to_float(row[inter + c]) * rs + (bias ? bias[inter + c] : 0.f), -limit), limit);
     out[i] = ni_from_float<T>(g / (1.0f + expf(-slope * g)) * (u + shift));
 }
 
 // The same, 16 bytes per thread (row widths that are multiples of 8 bfloat16 or 4 float values).
 template <typename T>
 __global__ void capped_glu_vec_kernel(const T* __restrict__ gate_up, T* __restrict__ out, long long n_vec, int inter,
-                                      float limit, float slope, float shift, const float* __restrict__ row_scale) {
+                                      float limit, float slope, float shift, const float* __restrict__ row_scale,
+                                      const float* __restrict__ bias) {
     constexpr int V = NiVec16<T>::N;
     const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= n_vec) return;
@@ -322,7 +330,8 @@ __global__ void capped_glu_vec_kernel(const T* __restrict__ gate_up, T* __restri
     const float rs = row_scale ? row_scale[t] : 1.0f;
 #pragma unroll
     for (int k = 0; k < V; ++k) {
-        const float gg = fminf(g[k] * rs, limit), uu = fminf(fmaxf(u[k] * rs, -limit), limit);
+        const float gg = fminf(g[k] * rs + (bias ? bias[c + k] : 0.f), limit);
+        const float uu = fminf(fmaxf(u[k] * rs + (bias ? bias[inter + c + k] : 0.f), -limit), limit);
         o[k] = gg / (1.0f + expf(-slope * gg)) * (uu + shift);
     }
     NiVec16<T>::store(out + (size_t)t * inter + c, o);
@@ -331,7 +340,7 @@ __global__ void capped_glu_vec_kernel(const T* __restrict__ gate_up, T* __restri
 // row_scale (FP32 [rows], or null): the row's gate and up values are multiplied by it before the limits, which is
 // what a unit computes when its INPUT was multiplied by that number (both products are linear in the input).
 NI_EXPORT int ni_capped_glu(const void* gate_up, void* out, int dtype, int n_rows, int inter, float limit, float slope,
-                            float shift, const float* row_scale, cudaStream_t stream) {
+                            float shift, const float* row_scale, const float* bias, cudaStream_t stream) {
     if (n_rows <= 0) return NI_OK;
     if (inter <= 0) return NI_ERR_BAD_ARGUMENT;
     const long long n = (long long)n_rows * inter, blocks = (n + 255) / 256;
@@ -339,20 +348,20 @@ NI_EXPORT int ni_capped_glu(const void* gate_up, void* out, int dtype, int n_row
     if (dtype == NI_DTYPE_BF16 && inter % 8 == 0) {
         const long long nv = n / 8;
         capped_glu_vec_kernel<__nv_bfloat16><<<(int)((nv + 255) / 256), 256, 0, stream>>>(
-            (const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, nv, inter, limit, slope, shift, row_scale);
+            (const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, nv, inter, limit, slope, shift, row_scale, bias);
         NI_RETURN_LAUNCH_STATUS();
     }
     if (dtype == NI_DTYPE_F32 && inter % 4 == 0) {
         const long long nv = n / 4;
         capped_glu_vec_kernel<float><<<(int)((nv + 255) / 256), 256, 0, stream>>>((const float*)gate_up, (float*)out, nv, inter,
-                                                                                limit, slope, shift, row_scale);
+                                                                                limit, slope, shift, row_scale, bias);
         NI_RETURN_LAUNCH_STATUS();
     }
     if (dtype == NI_DTYPE_F32)
-        capped_glu_kernel<float><<<(int)blocks, 256, 0, stream>>>((const float*)gate_up, (float*)out, n, inter, limit, slope, shift, row_scale);
+        capped_glu_kernel<float><<<(int)blocks, 256, 0, stream>>>((const float*)gate_up, (float*)out, n, inter, limit, slope, shift, row_scale, bias);
     else if (dtype == NI_DTYPE_BF16)
         capped_glu_kernel<__nv_bfloat16><<<(int)blocks, 256, 0, stream>>>((const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, n,
-                                                                         inter, limit, slope, shift, row_scale);
+                                                                         inter, limit, slope, shift, row_scale, bias);
     else return NI_ERR_BAD_ARGUMENT;
     NI_RETURN_LAUNCH_STATUS();
 }
@@ -451,5 +460,88 @@ NI_EXPORT int ni_relu_squared(const void* z, void* out, int dtype, long long n, 
         relu_squared_kernel<__nv_bfloat16><<<(int)blocks, 256, 0, stream>>>((const __nv_bfloat16*)z, (__nv_bfloat16*)out, n);
     else
         relu_squared_kernel<float><<<(int)blocks, 256, 0, stream>>>((const float*)z, (float*)out, n);
+    NI_RETURN_LAUNCH_STATUS();
+}
+
+
+// An embedding with a second table that is addressed by a hash of the token and the one before it:
+//   out[t, :] = table[token, :] + pairs[r, :],   r = (previous * mul_prev + token * mul_cur) mod buckets,
+// and r = buckets (the table's last row) for a sequence's first token.  The token before a step's first one is part of
+// the request's state: last[slot] holds the last token of the step before and is set to this step's last one by the
+// block that read it (the block of the request's first token in the step), so a step may be cut anywhere and a
+// captured step finds everything on the device.  One block per token; FP32 sum.
+template <typename T>
+__global__ void embedding_pairs_kernel(const int* __restrict__ tokens, const T* __restrict__ table, const T* __restrict__ pairs,
+                                       float* __restrict__ out, int d, int vocab, int buckets, int mul_prev, int mul_cur,
+                                       const int* __restrict__ positions, const int* __restrict__ seq_of_token,
+                                       const int* __restrict__ cu_q, const int* __restrict__ slots, int* __restrict__ last) {
+    __shared__ int s_row;
+    const int t = blockIdx.x;
+    const int tok = tokens[t];
+    if (threadIdx.x == 0) {
+        const int seq = seq_of_token[t], first = cu_q[seq];
+        int prev = 0;
+        if (t > first) {
+            prev = tokens[t - 1];
+        } else {
+            int* mine = last + slots[seq];
+            prev = *mine;
+            *mine = tokens[cu_q[seq + 1] - 1];
+        }
+        s_row = positions[t] == 0 ? buckets
+                                  : (int)(((long long)prev * mul_prev + (long long)tok * mul_cur) % (long long)buckets);
+    }
+    __syncthreads();
+    const bool ok = tok >= 0 && tok < vocab;
+    const int r = s_row < 0 ? s_row + buckets : s_row;
+    const T* row = table + (size_t)(ok ? tok : 0) * d;
+    const T* pr = pairs + (size_t)r * d;
+    float* o = out + (size_t)t * d;
+    for (int i = threadIdx.x; i < d; i += blockDim.x) o[i] = ok ? ni_to_float(row[i]) + ni_to_float(pr[i]) : 0.f;
+}
+
+// table [vocab, d] and pairs [buckets + 1, d] of one type; last int32 [slots].
+NI_EXPORT int ni_embedding_pairs(const int* tokens, const void* table, const void* pairs, int dtype, float* out, int n_tokens,
+                                 int d, int vocab, int buckets, int mul_prev, int mul_cur, const int* positions,
+                                 const int* seq_of_token, const int* cu_q, const int* slots, int* last, cudaStream_t stream) {
+    if (n_tokens <= 0) return NI_OK;
+    if (d <= 0 || vocab <= 0 || buckets <= 0) return NI_ERR_BAD_ARGUMENT;
+    const int threads = d >= 1024 ? 256 : 128;
+    if (dtype == NI_DTYPE_F32)
+        embedding_pairs_kernel<float><<<n_tokens, threads, 0, stream>>>(tokens, (const float*)table, (const float*)pairs, out, d,
+                                                                        vocab, buckets, mul_prev, mul_cur, positions,
+                                                                        seq_of_token, cu_q, slots, last);
+    else if (dtype == NI_DTYPE_BF16)
+        embedding_pairs_kernel<__nv_bfloat16><<<n_tokens, threads, 0, stream>>>(
+            tokens, (const __nv_bfloat16*)table, (const __nv_bfloat16*)pairs, out, d, vocab, buckets, mul_prev, mul_cur,
+            positions, seq_of_token, cu_q, slots, last);
+    else
+        return NI_ERR_BAD_ARGUMENT;
+    NI_RETURN_LAUNCH_STATUS();
+}
+
+// out = sa * a + sb * b, element by element (FP32; out may be a or b).
+__global__ void weighted_sum_kernel(const float* a, float sa, const float* b, float sb, float* out, long long n) {
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) out[i] = sa * a[i] + sb * b[i];
+}
+
+// The same, four numbers per thread (n a multiple of 4, all three on 16 bytes).
+__global__ void weighted_sum_vec_kernel(const float4* a, float sa, const float4* b, float sb, float4* out, long long n4) {
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n4) return;
+    const float4 x = a[i], y = b[i];
+    out[i] = make_float4(sa * x.x + sb * y.x, sa * x.y + sb * y.y, sa * x.z + sb * y.z, sa * x.w + sb * y.w);
+}
+
+NI_EXPORT int ni_weighted_sum(const float* a, float sa, const float* b, float sb, float* out, long long n, cudaStream_t stream) {
+    if (n <= 0) return NI_OK;
+    const bool wide = n % 4 == 0 && ((reinterpret_cast<size_t>(a) | reinterpret_cast<size_t>(b) | reinterpret_cast<size_t>(out)) & 15) == 0;
+    const long long items = wide ? n / 4 : n, blocks = (items + 255) / 256;
+    if (blocks > 2147483647LL) return NI_ERR_UNSUPPORTED_SIZE;
+    if (wide)
+        weighted_sum_vec_kernel<<<(int)blocks, 256, 0, stream>>>((const float4*)a, sa, (const float4*)b, sb, (float4*)out, items);
+    else
+        weighted_sum_kernel<<<(int)blocks, 256, 0, stream>>>(a, sa, b, sb, out, n);
     NI_RETURN_LAUNCH_STATUS();
 }

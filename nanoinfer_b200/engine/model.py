@@ -26,7 +26,11 @@ class DecoderModel:
         emb = config.embedding_spec()
         self.embedding = registry.part("embedding", emb.kind)(emb, d, by_scope.get(("embedding",), {}), rt)
         self.blocks = []
+        used = {run.layer for run in config.schedule}
         for i, layer in enumerate(config.layers):
+            if i not in used:                                  # no run names it: it has no weights and is not built
+                self.blocks.append(None)
+                continue
             cls = registry.part("arrangement", layer.arrangement)
             self.blocks.append(cls(layer, d, lambda what, i=i: by_scope.get(("layer", i, what), {}), rt))
             if hasattr(self.blocks[-1], "bind_embedding"):     # a block that reads a table the embedding owns

@@ -180,6 +180,17 @@ def _round_up(n: int, m: int) -> int:
     return -(-n // m) * m
 
 
+def with_sub_parts(part) -> list:
+    """``part`` and, if it is made of other parts (``sub_parts``: a mixer that runs several mixers side by side),
+    those too, to any depth: what the runner asks for kernel libraries, plans and graph safety."""
+    if part is None:
+        return []
+    out = [part]
+    for sub in getattr(part, "sub_parts", ()):
+        out += with_sub_parts(sub)
+    return out
+
+
 class ModelRunner:
     def __init__(self, config: ModelConfig, weights: Dict[str, torch.Tensor], *, dtype,
                  page_size: int = 16, num_pages=1024, max_requests: int = 8,
@@ -207,7 +218,8 @@ class ModelRunner:
         # for the bfloat16 path only; a class inherits its bases' lists).  Anything else is built when first used.
         bf16 = self.rt.dtype == torch.bfloat16
         needed = {"elementwise"} | ({"gemv_bf16", "gemv_ksplit"} if bf16 else {"gemm_f32"}) | ({"decode_fused"} if fused_decode else set())
-        all_parts = [p for b in self.model.blocks for p in (b, getattr(b, "mixer", None), getattr(b, "feed_forward", None))] \
+        all_parts = [q for b in self.model.blocks if b is not None
+                     for p in (b, getattr(b, "mixer", None), getattr(b, "feed_forward", None)) for q in with_sub_parts(p)] \
             + [self.model.embedding, self.model.head, self.model]
         for part in all_parts:
             if part is None:
@@ -272,9 +284,21 @@ class ModelRunner:
             if run.cache_of is not None:
                 src = self.caches[run.cache_of]
                 self.caches[r] = CacheView(group=src.group, pages=src.pages, state=src.state, writable=False)
+        # a state per request that belongs to no layer run: the embedding may keep one (``state_need`` /
+        # ``bind_state``), a row per request slot like the mixers' states, zeroed when the slot is handed out
+        self._part_states: List[torch.Tensor] = []
+        need = getattr(self.model.embedding, "state_need", lambda: None)()
+        if need is not None:
+            if not isinstance(need, StateNeed):
+                raise StepError("the embedding's state need must be a StateNeed")
+            dt = rt.dtype if need.dtype == "compute" else getattr(torch, need.dtype)
+            state = torch.zeros((max_requests,) + tuple(need.shape), dtype=dt, device=rt.device)
+            self.model.embedding.bind_state(state)
+            self._part_states.append(state)
         # hooks of the parts: who plans its own work per step, and what may be captured into a graph
-        parts = [p for b in self.model.blocks for p in (getattr(b, "mixer", None), getattr(b, "feed_forward", None))
-                 if p is not None] + [self.model.embedding, self.model.head]
+        parts = [q for b in self.model.blocks if b is not None
+                 for p in (getattr(b, "mixer", None), getattr(b, "feed_forward", None)) for q in with_sub_parts(p)] \
+            + [self.model.embedding, self.model.head]
         self.planners: List[type] = []
         for part in parts:
             owner = plan_owner(type(part))
@@ -378,6 +402,8 @@ class ModelRunner:
         slot = self.cache.admit(request)
         for r in self._state_runs:
             self.caches[r].state[slot].zero_()
+        for state in self._part_states:
+            state[slot].zero_()
         return slot
 
     N_FIXED = 7      # tokens, positions, request of each token, row offsets, kv lengths, slots, logit rows

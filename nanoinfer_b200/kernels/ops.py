@@ -34,7 +34,7 @@ _SIGNATURES = {
         "ni_rope_kv_write": [_P, _I, _P, _P, _P, _P, _P, _P, _I, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P],
     },
     "attention_generic": {
-        "ni_attention_generic": [_P, _I, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _F, _P, _F, _I, _P],
+        "ni_attention_generic": [_P, _I, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _F, _P, _F, _I, _I, _I, _P],
     },
     "gemm_f32": {
         "ni_gemm_f32": [_P, _P, _P, _I, _I, _I, _P],
@@ -43,21 +43,25 @@ _SIGNATURES = {
     "pointwise": {
         "ni_embedding_sinusoid": [_P, _P, _P, _I, _P, _P, _I, _I, _I, _P],
         "ni_cast_bf16": [_P, _P, _LL, _P],
-        "ni_add_normed": [_P, _P, _I, _P, _F, _I, _I, _P],
+        "ni_add_normed": [_P, _P, _I, _P, _F, _I, _I, _P, _P],
         "ni_polynorm": [_P, _I, _P, _F, _P, _I, _I, _P],
         "ni_gelu_table_gate": [_P, _I, _P, _P, _I, _P, _I, _I, _I, _I, _I, _P],
         "ni_add_row": [_P, _P, _I, _I, _I, _P],
         "ni_embedding_scaled": [_P, _P, _I, _F, _P, _I, _I, _I, _P],
         "ni_scale_f32": [_P, _F, _LL, _P],
-        "ni_capped_glu": [_P, _P, _I, _I, _I, _F, _F, _F, _P, _P],
+        "ni_capped_glu": [_P, _P, _I, _I, _I, _F, _F, _F, _P, _P, _P],
         "ni_concat_cast": [_P, _P, _P, _I, _I, _I, _P],
         "ni_relu_squared": [_P, _P, _I, _LL, _P],
+        "ni_weighted_sum": [_P, _F, _P, _F, _P, _LL, _P],
+        "ni_embedding_pairs": [_P, _P, _P, _I, _P, _I, _I, _I, _I, _I, _I, _P, _P, _P, _P, _P, _P],
     },
     "qk_norm_rope": {
-        "ni_qk_norm_rope": [_P, _I, _I, _P, _P, _P, _F, _P, _P, _P, _I, _P, _F, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P],
+        "ni_qk_norm_rope": [_P, _I, _I, _P, _P, _P, _F, _P, _P, _P, _I, _P, _F, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P],
     },
     "lightning": {
-        "ni_lightning_recurrence": [_P, _I, _I, _P, _LL, _P, _P, _P, _P, _I, _I, _I, _P, _LL, _I, _I, _I, _P],
+        "ni_lightning_recurrence": [_P, _I, _I, _P, _LL, _P, _P, _P, _P, _I, _I, _I, _P, _LL, _I, _I, _I, _I, _P],
+        "ni_linear_attention_prepare": [_P, _I, _I, _P, _P, _F, _P, _I, _I, _I, _I, _I, _P],
+        "ni_group_gated_norm": [_P, _P, _I, _I, _I, _P, _F, _P, _I, _I, _I, _I, _P],
         "ni_lightning_max_chunks": [_I, _I],
         "ni_lightning_gated_norm": [_P, _P, _I, _I, _I, _P, _F, _P, _I, _I, _P],
     },
@@ -81,6 +85,7 @@ _SIGNATURES = {
     "latent": {
         "ni_latent_norm_write": [_P, _I, _I, _I, _P, _F, _P, _P, _P, _P, _I, _I, _I, _I, _P],
         "ni_head_gate": [_P, _I, _P, _I, _I, _I, _I, _I, _P],
+        "ni_latent_rope_write": [_P, _I, _I, _I, _P, _F, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P, _I, _P, _I, _P],
     },
     "gemv_bf16": {
         "ni_gemv_bf16": [_P, _P, _P, _I, _I, _I, _I, _P, _LL, _P, _P, _P, _I, _P, _I, _F, _P],
@@ -341,12 +346,14 @@ def attention_generic(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Ten
                       block_table: torch.Tensor, n_q_heads: int, n_kv_heads: int, head_dim: int,
                       page_size: int, window: Optional[int], scale: float,
                       token_list: Optional[torch.Tensor] = None, head_slopes: Optional[torch.Tensor] = None,
-                      score_cap: float = 0.0, value_dim: Optional[int] = None) -> None:
+                      score_cap: float = 0.0, value_dim: Optional[int] = None, chunk: int = 0,
+                      sink: bool = False) -> None:
     """The plain attention kernel (any dtype, any head size up to 512).  ``token_list``
     int32 [n] restricts it to those tokens of the step.  ``head_slopes`` float32 [Hq] adds
     slope[h] * (key position - query position) to the scaled scores of head h.  ``score_cap`` c > 0
     bounds the scaled scores: s <- c * tanh(s / c).  ``value_dim``: the size of a value where it differs
-    from the keys' (value pages [P, Hkv, page_size, value_dim], out [T, Hq * value_dim])."""
+    from the keys' (value pages [P, Hkv, page_size, value_dim], out [T, Hq * value_dim]).  ``chunk`` c > 0: a token at
+    position p sees only the keys from p - p % c on.  ``sink``: one is added to the softmax's denominator."""
     if head_slopes is not None and head_slopes.numel() != n_q_heads:
         raise KernelError("attention: one slope per query head")
     n = q.shape[0]
@@ -367,7 +374,7 @@ def attention_generic(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Ten
         block_table.shape[1], n if token_list is None else token_list.numel(), n_q_heads, n_kv_heads, head_dim, page_size,
         int(window) if window else 0, float(scale),
         _dev(head_slopes, "head_slopes", torch.float32) if head_slopes is not None else None, float(score_cap),
-        v_dim, _stream()), "attention_generic")
+        v_dim, int(chunk or 0), 1 if sink else 0, _stream()), "attention_generic")
 
 
 def gemm_f32(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
@@ -414,13 +421,15 @@ def cast_bf16(x: torch.Tensor, out: torch.Tensor) -> None:
                                           _stream()), "cast_bf16")
 
 
-def add_normed(h: torch.Tensor, y: torch.Tensor, weight: torch.Tensor, eps: float) -> None:
-    """h += y / sqrt(mean(y^2) + eps) * weight, row by row; h float32 [T, d], weight float32 [d]."""
+def add_normed(h: torch.Tensor, y: torch.Tensor, weight: torch.Tensor, eps: float, bias: Optional[torch.Tensor] = None) -> None:
+    """h += z / sqrt(mean(z^2) + eps) * weight, row by row, with z = y (+ ``bias`` float32 [d], if given); h float32
+    [T, d], weight float32 [d]."""
     n, d = h.shape
-    if y.shape != h.shape or weight.numel() != d:
+    if y.shape != h.shape or weight.numel() != d or (bias is not None and bias.numel() != d):
         raise KernelError("add_normed: shapes do not agree")
     _check(load("pointwise").ni_add_normed(_dev(h, "h", torch.float32), _dev(y, "y"), _code(y, "y"),
-                                           _dev(weight, "weight", torch.float32), float(eps), n, d, _stream()), "add_normed")
+                                           _dev(weight, "weight", torch.float32), float(eps), n, d,
+                                           _dev(bias, "bias", torch.float32) if bias is not None else None, _stream()), "add_normed")
 
 
 def polynorm(z: torch.Tensor, coef: torch.Tensor, eps: float, out: torch.Tensor) -> None:
@@ -503,6 +512,26 @@ def latent_norm_write(proj, col0, rank, weight, eps, pages, positions, seq_of_to
         block_table.shape[1], n, rank, page_size, _stream()), "latent_norm_write")
 
 
+def latent_rope_write(proj, col0, rank, rot_dim, weight, eps, pages, positions, seq_of_token, block_table, page_size,
+                      inv_freq, interleaved, q, n_heads) -> None:
+    """A latent cache row with a rotated key part: pages[page of t, place of t, :] = [RMSNorm(proj[t, col0 : col0 +
+    rank]) * weight | rot(proj[t, col0 + rank : col0 + rank + rot_dim])], pages [P, page_size, rank + rot_dim] (None:
+    nothing is written); the last rot_dim dimensions of every head of q [T, H (rank + rot_dim)] are rotated in place.
+    Pairs (2i, 2i + 1) if ``interleaved`` else (i, i + rot_dim / 2); angle float(position) * inv_freq[i]."""
+    n = proj.shape[0]
+    w = rank + rot_dim
+    if (pages is not None and (tuple(pages.shape[1:]) != (page_size, w) or pages.dtype != proj.dtype)) or \
+            weight.numel() != rank or tuple(q.shape) != (n, n_heads * w) or q.dtype != proj.dtype or \
+            (rot_dim > 0 and inv_freq.numel() != rot_dim // 2):
+        raise KernelError("latent_rope_write: pages must be [P, page_size, rank + rot_dim] and q [T, H (rank + rot_dim)] of proj's dtype")
+    _check(load("latent").ni_latent_rope_write(
+        _dev(proj, "proj"), _code(proj, "proj"), proj.shape[1], int(col0), _dev(weight, "weight", torch.float32),
+        float(eps), _dev(pages, "pages") if pages is not None else None, _dev(positions, "positions", torch.int32),
+        _dev(seq_of_token, "seq_of_token", torch.int32), _dev(block_table, "block_table", torch.int32),
+        block_table.shape[1], n, rank, rot_dim, page_size, _dev(inv_freq, "inv_freq", torch.float32),
+        1 if interleaved else 0, _dev(q, "q"), n_heads, _stream()), "latent_rope_write")
+
+
 def head_gate(x, proj, col0, n_heads, vdim) -> None:
     """x[t, h, :] *= sigmoid(proj[t, col0 + h]) in place; x [T, H V]."""
     n = x.shape[0]
@@ -522,6 +551,30 @@ def embedding_scaled(tokens: torch.Tensor, table: torch.Tensor, scale: float, ou
                                                  n, d, table.shape[0], _stream()), "embedding_scaled")
 
 
+def embedding_pairs(tokens, table, pairs, out, buckets, mul_prev, mul_cur, positions, seq_of_token, cu_q, slots, last) -> None:
+    """out[t, :] = float32(table[tokens[t]]) + float32(pairs[r]) with r = (previous token * mul_prev + token * mul_cur) mod
+    buckets, or r = buckets for a token at position 0; the token before a step's first one is read from ``last``
+    (int32 [slots], one per request slot), which is then set to the request's last token of this step."""
+    n, d = out.shape
+    if tokens.numel() != n or table.shape[1] != d or tuple(pairs.shape) != (buckets + 1, d) or pairs.dtype != table.dtype:
+        raise KernelError("embedding_pairs: shapes or dtypes do not agree")
+    i32 = torch.int32
+    _check(load("pointwise").ni_embedding_pairs(
+        _dev(tokens, "tokens", i32), _dev(table, "table"), _dev(pairs, "pairs"), _code(table, "table"),
+        _dev(out, "out", torch.float32), n, d, table.shape[0], int(buckets), int(mul_prev), int(mul_cur),
+        _dev(positions, "positions", i32), _dev(seq_of_token, "seq_of_token", i32), _dev(cu_q, "cu_q", i32),
+        _dev(slots, "slots", i32), _dev(last, "last", i32), _stream()), "embedding_pairs")
+
+
+def weighted_sum(a: torch.Tensor, sa: float, b: torch.Tensor, sb: float, out: torch.Tensor) -> None:
+    """out = sa * a + sb * b, element by element; all float32 of one shape (out may be a or b)."""
+    if a.shape != b.shape or out.shape != a.shape:
+        raise KernelError("weighted_sum: shapes do not agree")
+    f32 = torch.float32
+    _check(load("pointwise").ni_weighted_sum(_dev(a, "a", f32), float(sa), _dev(b, "b", f32), float(sb), _dev(out, "out", f32),
+                                             a.numel(), _stream()), "weighted_sum")
+
+
 def add_row(h: torch.Tensor, row: torch.Tensor) -> None:
     """h[t, :] += row for every t; h float32 [T, d], row [d] (float32 or bfloat16)."""
     n, d = h.shape
@@ -537,16 +590,18 @@ def scale_f32(x: torch.Tensor, factor: float) -> None:
 
 
 def capped_glu(gate_up: torch.Tensor, out: torch.Tensor, limit: float, slope: float, shift: float,
-               row_scale: Optional[torch.Tensor] = None) -> None:
-    """out = g * sigmoid(slope * g) * (u + shift) with g = min(r gate, limit), u = clamp(r up, -limit, limit);
-    gate_up = [gate | up] [T, 2I], out [T, I], one dtype; ``row_scale`` float32 [T]: r per row (else 1) - what the
-    unit computes when its input was multiplied by r."""
+               row_scale: Optional[torch.Tensor] = None, bias: Optional[torch.Tensor] = None) -> None:
+    """out = g * sigmoid(slope * g) * (u + shift) with g = min(r gate + b_gate, limit), u = clamp(r up + b_up, -limit,
+    limit); gate_up = [gate | up] [T, 2I], out [T, I], one dtype; ``row_scale`` float32 [T]: r per row (else 1) - what
+    the unit computes when its input was multiplied by r; ``bias`` float32 [2I] (gate then up; else none)."""
     n, inter = out.shape
-    if gate_up.shape != (n, 2 * inter) or gate_up.dtype != out.dtype or (row_scale is not None and row_scale.numel() != n):
-        raise KernelError("capped_glu: gate_up must be [T, 2I] of out's dtype (and row_scale [T])")
+    if gate_up.shape != (n, 2 * inter) or gate_up.dtype != out.dtype or (row_scale is not None and row_scale.numel() != n) \
+            or (bias is not None and bias.numel() != 2 * inter):
+        raise KernelError("capped_glu: gate_up must be [T, 2I] of out's dtype (row_scale [T], bias [2I])")
     _check(load("pointwise").ni_capped_glu(_dev(gate_up, "gate_up"), _dev(out, "out"), _code(out, "out"), n, inter,
                                            float(limit), float(slope), float(shift),
                                            _dev(row_scale, "row_scale", torch.float32) if row_scale is not None else None,
+                                           _dev(bias, "bias", torch.float32) if bias is not None else None,
                                            _stream()), "capped_glu")
 
 
@@ -568,11 +623,12 @@ def relu_squared(z: torch.Tensor, out: torch.Tensor) -> None:
 
 
 def qk_norm_rope(qkv, bias, q_gain, k_gain, eps, positions, seq_of_token, block_table, inv_freq, magnitude, q_out,
-                 k_pages, v_pages, n_heads, n_kv_heads, head_dim, value_dim, rotary_dim, page_size) -> None:
+                 k_pages, v_pages, n_heads, n_kv_heads, head_dim, value_dim, rotary_dim, page_size, head_unit=False) -> None:
     """From the fused projection ``qkv`` [T, ld] (columns q | k | v): + ``bias`` (float32 over those columns, or
     None); RMS norm of all the row's query values together and of all its key values together (``q_gain`` float32
     [H hd], ``k_gain`` float32 [Hkv hd]; both None: no norm); rotation of the first ``rotary_dim`` dimensions of every
-    head, dimension i paired with i + rotary_dim / 2, cosine and sine times ``magnitude``; queries -> q_out [T, H hd],
+    head, dimension i paired with i + rotary_dim / 2, cosine and sine times ``magnitude``; with ``head_unit`` every
+    head of q and k is then divided by its own root mean square (``eps`` inside the root, no weight); queries -> q_out [T, H hd],
     keys -> k_pages [P, Hkv, page_size, hd], values -> v_pages [P, Hkv, page_size, value_dim] (None: nothing written)."""
     n = qkv.shape[0]
     f32, i32 = torch.float32, torch.int32
@@ -594,7 +650,7 @@ def qk_norm_rope(qkv, bias, q_gain, k_gain, eps, positions, seq_of_token, block_
         float(eps), _dev(positions, "positions", i32), _dev(seq_of_token, "seq_of_token", i32),
         _dev(block_table, "block_table", i32), block_table.shape[1], _dev(inv_freq, "inv_freq", f32), float(magnitude),
         _dev(q_out, "q_out"), _dev(k_pages, "k_pages") if write else None, _dev(v_pages, "v_pages") if write else None,
-        n, n_heads, n_kv_heads, head_dim, value_dim, rotary_dim, page_size, _stream()), "qk_norm_rope")
+        n, n_heads, n_kv_heads, head_dim, value_dim, rotary_dim, page_size, 1 if head_unit else 0, _stream()), "qk_norm_rope")
 
 
 LIGHTNING_MAX_DIM = 256      # the largest key size whose chunk buffers fit a block's shared memory
@@ -607,14 +663,18 @@ def lightning_max_chunks(n_tokens: int, n_seqs: int) -> int:
     return int(load("lightning").ni_lightning_max_chunks(int(n_tokens), int(n_seqs)))
 
 
-def lightning_recurrence(proj, state, cu_q, slots, n_seqs, decay, n_heads, dim, vdim, out, max_q_len=None, buf=None) -> None:
+def lightning_recurrence(proj, state, cu_q, slots, n_seqs, decay, n_heads, dim, vdim, out, max_q_len=None, buf=None,
+                         activation: bool = True) -> None:
     """Linear attention with a decay per head over a step's tokens, request by request: with q, k [H, dim] and v
     [H, vdim] = silu of proj's columns (q | k | v | ...), S <- decay_h S + k v^T and out = S^T q, all float32;
     ``state`` float32 [slots, >= H dim vdim] holds every request's S and advances by the step's tokens; out float32
     [T, H vdim].  ``max_q_len``: the most tokens one request brings (None: as many as there are tokens); a step
     of single tokens is one launch, others run in chunks and need ``buf`` (float32, lightning_max_chunks(T, n_seqs)
-    x H dim vdim entries; None: allocated here)."""
+    x H dim vdim entries; None: allocated here).  ``activation`` False: proj (float32) holds q, k and v themselves -
+    nothing is activated (a caller that has prepared them, e.g. rotated queries and scaled keys)."""
     n = proj.shape[0]
+    if not activation and proj.dtype != torch.float32:
+        raise KernelError("lightning_recurrence: q, k, v that enter as they are must be float32")
     if proj.shape[1] < n_heads * (2 * dim + vdim) or out.shape != (n, n_heads * vdim) or decay.numel() != n_heads \
             or state.shape[1] < n_heads * dim * vdim:
         raise KernelError("lightning_recurrence: shapes do not agree")
@@ -631,7 +691,34 @@ def lightning_recurrence(proj, state, cu_q, slots, n_seqs, decay, n_heads, dim, 
         _dev(proj, "proj"), _code(proj, "proj"), proj.shape[1], _dev(state, "state", torch.float32), state.shape[1],
         _dev(cu_q, "cu_q", torch.int32), _dev(slots, "slots", torch.int32), _dev(decay, "decay", torch.float32),
         _dev(out, "out", torch.float32), n, n_seqs, max_q_len, _dev(buf, "buf", torch.float32) if chunks else None,
-        chunks, n_heads, dim, vdim, _stream()), "lightning_recurrence")
+        chunks, n_heads, dim, vdim, 1 if activation else 0, _stream()), "lightning_recurrence")
+
+
+def linear_attention_prepare(proj, positions, inv_freq, k_scale, qkv, n_heads, dim, vdim, rotary_dim) -> None:
+    """qkv[t] = [rot(q) | rot(k) * k_scale | v] in float32 from proj [T, ld] (columns q (H dim) | k (H dim) | v (H vdim)
+    | ...): the first ``rotary_dim`` dimensions of every head of q and k are rotated, dimension i paired with
+    i + rotary_dim / 2, by the angle float(position) * inv_freq[i]; the values are copied."""
+    n = proj.shape[0]
+    cols = n_heads * (2 * dim + vdim)
+    if proj.shape[1] < cols or tuple(qkv.shape) != (n, cols) or (rotary_dim > 0 and inv_freq.numel() != rotary_dim // 2):
+        raise KernelError("linear_attention_prepare: shapes do not agree")
+    _check(load("lightning").ni_linear_attention_prepare(
+        _dev(proj, "proj"), _code(proj, "proj"), proj.shape[1], _dev(positions, "positions", torch.int32),
+        _dev(inv_freq, "inv_freq", torch.float32), float(k_scale), _dev(qkv, "qkv", torch.float32), n, n_heads, dim, vdim,
+        int(rotary_dim), _stream()), "linear_attention_prepare")
+
+
+def group_gated_norm(o, proj, col0, weight, eps, y, group: int, gate: str = "sigmoid") -> None:
+    """y = o / sqrt(mean over each group of ``group`` neighbouring columns of o^2 + eps) * weight * act(proj[:, col0 :
+    col0 + N]); o float32 [T, N], weight float32 [N] or None (1), y [T, N] of proj's dtype; ``gate`` "sigmoid" or "silu"."""
+    n, width = o.shape
+    if y.shape != o.shape or y.dtype != proj.dtype or proj.shape[0] != n or group <= 0 or width % group or \
+            (weight is not None and weight.numel() != width) or gate not in ("sigmoid", "silu"):
+        raise KernelError("group_gated_norm: shapes, dtypes or the gate's kind do not agree")
+    _check(load("lightning").ni_group_gated_norm(
+        _dev(o, "o", torch.float32), _dev(proj, "proj"), _code(proj, "proj"), proj.shape[1], int(col0),
+        _dev(weight, "weight", torch.float32) if weight is not None else None, float(eps), _dev(y, "y"), n, width // group,
+        int(group), 1 if gate == "silu" else 0, _stream()), "group_gated_norm")
 
 
 def lightning_gated_norm(o, proj, col0, weight, eps, y) -> None:

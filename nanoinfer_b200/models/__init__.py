@@ -1,2 +1,2 @@
 """Architectures: each module registers its config parser and tensor naming."""
-from . import llama, runevik, tazulix, vuvalorn  # noqa: F401
+from . import llama, mobatar, runevik, tazulix, vuvalorn  # noqa: F401

@@ -271,6 +271,70 @@ class SandwichNormBlock:
         return None
 
 
+class OutputNormBlock:
+    """h += norm1(mixer(h));  h += norm2(ffn(h)): the sublayers read the stream itself, and only their OUTPUT passes a
+    norm before it joins the stream (``LayerSpec.mixer_norm`` is the norm on the mixer's output, ``ffn_norm`` the one
+    on the feed-forward's; a layer may have no feed-forward).  The stream, the norms' statistics and the additions are
+    FP32; a sublayer reads the stream rounded to the compute type (FP32: the stream itself) and hands its output over
+    in FP32 where its last product can.  A feed-forward whose last projection has a bias (``output_bias``) leaves it
+    to the kernel that norms and adds the output."""
+
+    kernel_modules = ("pointwise",)       # libraries of csrc that this part's kernels live in
+
+    def __init__(self, layer_spec, hidden_size: int, weights_of, rt) -> None:
+        self.rt, self.hidden_size = rt, hidden_size
+        self.mixer_norm = part("norm", layer_spec.mixer_norm.kind)(layer_spec.mixer_norm, hidden_size, weights_of("mixer_norm"), rt)
+        self.mixer = part("mixer", layer_spec.mixer.kind)(layer_spec.mixer, hidden_size, weights_of("mixer"), rt)
+        self.feed_forward = self.ffn_norm = None
+        if layer_spec.feed_forward is not None:
+            if layer_spec.ffn_norm is None:
+                raise ValueError("an output-norm layer's feed-forward needs its norm")
+            self.ffn_norm = part("norm", layer_spec.ffn_norm.kind)(layer_spec.ffn_norm, hidden_size, weights_of("ffn_norm"), rt)
+            self.feed_forward = part("feed_forward", layer_spec.feed_forward.kind)(
+                layer_spec.feed_forward, hidden_size, weights_of("feed_forward"), rt)
+        for norm in (self.mixer_norm, self.ffn_norm):
+            if norm is not None and not rt.fuses_norm(norm):
+                raise ValueError("an output-norm layer's norms must be RMS norms with a gain per coordinate")
+
+    def weights_in_order(self) -> tuple:
+        ffn = self.feed_forward
+        return tuple(getattr(self.mixer, "weights_in_order", tuple)()) + \
+            (tuple(getattr(ffn, "weights_in_order", tuple)()) if ffn is not None else ())
+
+    def first_norm(self):
+        return None
+
+    def _input(self, h: torch.Tensor) -> torch.Tensor:
+        if self.rt.dtype == torch.float32:
+            return h
+        x = self.rt.empty(h.shape[0], self.hidden_size)
+        ops.cast_bf16(h, x)
+        return x
+
+    def forward(self, h: torch.Tensor, delta, ctx, cache):
+        if isinstance(delta, NormHandoff):
+            delta = None                                   # the stream is up to date; nothing here reads a prepared norm
+        if delta is not None:
+            ops.residual_add(h, delta)
+        after = ctx.read_after                       # what runs after this block
+        ffn = self.feed_forward
+        ctx.read_after = (tuple(getattr(ffn, "weights_in_order", tuple)()) if ffn is not None else ()) + tuple(after)
+        try:
+            y = self.mixer.forward(self._input(h), ctx, cache)
+        finally:
+            ctx.read_after = after
+        ops.add_normed(h, y, self.mixer_norm.gain, self.mixer_norm.eps)
+        if ffn is not None:
+            bias = getattr(ffn, "output_bias", None)
+            if bias is not None:
+                y = ffn.forward(self._input(h), ctx, bias_taken=True)
+            else:
+                y = ffn.forward(self._input(h), ctx)
+            ops.add_normed(h, y, self.ffn_norm.gain, self.ffn_norm.eps, bias=bias)
+        return None
+
+
 register_part("arrangement", "pre_norm", PreNormBlock, replace=True)
+register_part("arrangement", "output_norm", OutputNormBlock, replace=True)
 register_part("arrangement", "sandwich_norm", SandwichNormBlock, replace=True)
 register_part("arrangement", "parallel", ParallelBlock, replace=True)

@@ -6,7 +6,7 @@ import torch
 
 from ..config.registry import register_part
 from ..kernels import ops
-from .base import Part, WeightSlot
+from .base import Part, StateNeed, WeightSlot
 
 
 class TableEmbedding(Part):
@@ -73,5 +73,53 @@ class SinusoidTableEmbedding(Part):
         ops.embedding_sinusoid(tokens, ctx.positions, self.table, self.inv_freq, h)
 
 
+class PairHashEmbedding(Part):
+    """Row ``id`` of a [vocab, hidden] table plus a row of a second table [buckets + 1, hidden] that is chosen by the
+    token AND the one before it: row (previous * mul_prev + id * mul_cur) mod buckets, and the last row (number
+    ``buckets``) for a sequence's first token.  ``buckets``, ``mul_prev`` and ``mul_cur`` come in the spec's extra.
+
+    The token before a step's first one belongs to the request's state: one int32 per request slot, kept by the
+    runner beside the mixers' states (``state_need`` / ``bind_state``), read and advanced by the embedding's one
+    kernel - so a step may be cut anywhere, and a captured step finds its predecessor on the device."""
+
+    kernel_modules = ("pointwise",)       # libraries of csrc that this part's kernels live in
+
+    graph_safe = "all"
+    wants_context = True        # forward(tokens, h, ctx): it reads positions, request offsets and slots
+
+    @staticmethod
+    def _dims(spec):
+        e = spec.extra_dict()
+        return int(e["buckets"]), int(e["mul_prev"]), int(e["mul_cur"])
+
+    @staticmethod
+    def weight_slots(spec, hidden_size):
+        buckets, _, _ = PairHashEmbedding._dims(spec)
+        return {"weight": WeightSlot((spec.vocab_size, hidden_size)), "pairs": WeightSlot((buckets + 1, hidden_size))}
+
+    def __init__(self, spec, hidden_size, weights, rt) -> None:
+        super().__init__(spec, hidden_size, weights, rt)
+        self.buckets, self.mul_prev, self.mul_cur = self._dims(spec)
+        if self.buckets <= 0:
+            raise ValueError("a pair-hash embedding needs at least one bucket")
+        self.table = rt.weight(weights["weight"])
+        self.pairs = rt.weight(weights["pairs"])
+        self.last = None
+
+    def state_need(self):
+        return StateNeed((1,), "int32")
+
+    def bind_state(self, state) -> None:
+        """``state``: int32 [request slots, 1], zeroed by the runner when a slot is handed out."""
+        self.last = state
+
+    def forward(self, tokens, h, ctx) -> None:
+        if self.last is None:
+            raise ValueError("a pair-hash embedding needs its per-request state (the runner binds it)")
+        ops.embedding_pairs(tokens, self.table, self.pairs, h, self.buckets, self.mul_prev, self.mul_cur, ctx.positions,
+                            ctx.seq_of_token, ctx.cu_q, ctx.slots, self.last)
+
+
 register_part("embedding", "table", TableEmbedding, replace=True)
+register_part("embedding", "table_pair_hash", PairHashEmbedding, replace=True)
 register_part("embedding", "table_sinusoid", SinusoidTableEmbedding, replace=True)

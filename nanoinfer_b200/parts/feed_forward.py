@@ -138,7 +138,10 @@ class PolyNorm(Part):
 class CappedGLU(Part):
     """A gated unit whose arguments are capped: g = min(W_gate x, limit), u = clamp(W_up x, -limit, limit),
     y = W_down (g * sigmoid(gate_slope * g) * (u + up_shift)); ``limit``, ``gate_slope`` and ``up_shift`` come in
-    the spec's extra.  Gate and up are one product; the output leaves in FP32 (the arrangement norms it)."""
+    the spec's extra.  Gate and up are one product; the output leaves in FP32 (the arrangement norms it).
+    With ``bias`` in the extra all three projections have one ("gate.b", "up.b", "down.b"): gate's and up's are added
+    in FP32 before the limits by the activation kernel; the down projection's is left to whoever takes the output
+    (``output_bias``: an arrangement that norms the output adds it inside that kernel; otherwise it is added here)."""
 
     kernel_modules = ("pointwise",)       # libraries of csrc that this part's kernels live in
 
@@ -148,8 +151,11 @@ class CappedGLU(Part):
     @staticmethod
     def weight_slots(spec, hidden_size: int) -> Dict[str, WeightSlot]:
         i = spec.intermediate_size
-        return {"gate": WeightSlot((i, hidden_size)), "up": WeightSlot((i, hidden_size)),
-                "down": WeightSlot((hidden_size, i))}
+        slots = {"gate": WeightSlot((i, hidden_size)), "up": WeightSlot((i, hidden_size)),
+                 "down": WeightSlot((hidden_size, i))}
+        if spec.extra_dict().get("bias", False):
+            slots.update({"gate.b": WeightSlot((i,)), "up.b": WeightSlot((i,)), "down.b": WeightSlot((hidden_size,))})
+        return slots
 
     def __init__(self, spec, hidden_size, weights, rt) -> None:
         super().__init__(spec, hidden_size, weights, rt)
@@ -159,12 +165,16 @@ class CappedGLU(Part):
         self.slope, self.shift = float(e.get("gate_slope", 1.0)), float(e.get("up_shift", 0.0))
         self.w_gate_up = rt.weight(torch.cat([weights["gate"], weights["up"]], dim=0))
         self.w_down = rt.weight(weights["down"])
+        self.bias_gate_up = self.output_bias = None
+        if e.get("bias", False):
+            self.bias_gate_up = rt.gain(torch.cat([weights["gate.b"], weights["up.b"]]))
+            self.output_bias = rt.gain(weights["down.b"])
 
     def weights_in_order(self) -> tuple:
         return (self.w_gate_up, self.w_down)
 
-    def forward(self, x: torch.Tensor, ctx):
-        return self.finish(self.rt.linear(x, self.w_gate_up), ctx)
+    def forward(self, x: torch.Tensor, ctx, bias_taken: bool = False):
+        return self.finish(self.rt.linear(x, self.w_gate_up), ctx, bias_taken=bias_taken)
 
     def project(self, h: torch.Tensor, norm) -> torch.Tensor:
         """gate | up of norm(h) with the norm inside the product (steps of a few rows)."""
@@ -172,11 +182,15 @@ class CappedGLU(Part):
         ops.gemv_norm_bf16(h, norm.gain, norm.eps, None, self.w_gate_up, z, ops.STORE_BF16)
         return z
 
-    def finish(self, gate_up: torch.Tensor, ctx):
+    def finish(self, gate_up: torch.Tensor, ctx, bias_taken: bool = False):
+        """``bias_taken``: the caller adds ``output_bias`` itself (inside the kernel that norms the output)."""
         rt = self.rt
         act = rt.empty(gate_up.shape[0], self.inter)
-        ops.capped_glu(gate_up, act, self.limit, self.slope, self.shift)
-        return rt.linear(act, self.w_down, out_dtype=torch.float32)
+        ops.capped_glu(gate_up, act, self.limit, self.slope, self.shift, bias=self.bias_gate_up)
+        y = rt.linear(act, self.w_down, out_dtype=torch.float32)
+        if self.output_bias is not None and not bias_taken:
+            ops.add_row(y, self.output_bias)
+        return y
 
 
 class SquaredReLU(Part):

@@ -15,7 +15,8 @@ from .base import PagedKVNeed, PagedNeed, Part, StateNeed, StepPlan, WeightSlot
 class PagedAttendMixin:
     """What every mixer that attends over pages of keys and values shares: the step's plan (which tokens
     go to which kernel) and the choice among the attention kernels.  A class that uses it sets n_heads,
-    n_kv, head_dim, window, scale, position and w_o."""
+    n_kv, head_dim, window, scale, position and w_o; optionally ``chunk`` (c > 0: a token at position p sees only the
+    keys from p - p % c on) and ``sink`` (one is added to the softmax's denominator)."""
 
     # How the attention kernels split a step.  Requests that bring at most SHORT_PORTION tokens are
     # handled token by token by the split-K kernel (which fetches a token's last
@@ -53,6 +54,10 @@ class PagedAttendMixin:
                          "tile_row0": np.asarray([t[2] for t in tiles], dtype=i32)},
                         {"n_dec": len(dec), "n_tiles": len(tiles)})
 
+    def _fast_attention(self, chunk: int, sink: bool) -> bool:
+        """True if the tensor-core attention kernels compute this mixer's mask and denominator."""
+        return chunk == 0 and not sink
+
     def _attend(self, q, cache, att, ctx, table) -> None:
         """Attention of every token of the step over its own request's pages.
 
@@ -64,11 +69,12 @@ class PagedAttendMixin:
         n = q.shape[0]
         slopes = getattr(self.position, "head_slopes", None)
         cap = float(getattr(self, "score_cap", 0.0))       # > 0: scores are bounded by cap * tanh(s / cap)
-        if rt.dtype != torch.bfloat16 or slopes is not None:
-            # float32, or a position encoding that acts on the scores (a bias slope[h] * (k_pos - q_pos)):
-            # the plain kernel takes both; the tensor-core kernels know rotations and a cap on the scores
+        chunk, sink = int(getattr(self, "chunk", 0) or 0), bool(getattr(self, "sink", False))
+        if rt.dtype != torch.bfloat16 or slopes is not None or not self._fast_attention(chunk, sink):
+            # float32, or a position encoding that acts on the scores (a bias slope[h] * (k_pos - q_pos)), or a mask
+            # or denominator that the tensor-core kernels do not know: the plain kernel takes them all
             ops.attention_generic(q, cache.k_pages, cache.v_pages, att, ctx.positions, ctx.seq_of_token,
-                                  table, *common, head_slopes=slopes, score_cap=cap)
+                                  table, *common, head_slopes=slopes, score_cap=cap, chunk=chunk, sink=sink)
             return
         decode_ok = self.head_dim in ops.DECODE_HEAD_DIMS and self.n_heads // self.n_kv <= 16
         prefill_ok = self.head_dim % 16 == 0 and self.head_dim <= ops.PREFILL_MAX_HEAD_DIM
@@ -230,11 +236,21 @@ class LatentAttention(PagedAttendMixin, Part):
     sigmoid(W_g x)_h (one gate per head), then W_o.  A layer with ``own_latent`` false stores nothing: it
     reads the pages of the run it shares a cache with (``LayerRun.cache_of``) through its own W_uk, W_uv.
 
+    Options in the spec's extra.  ``rope_dim`` = n > 0: every head's query has n more dimensions behind its ``head_dim``
+    unrotated ones (W_q has heads x (head_dim + n) rows), W_dkv has n more rows behind the latent's (not normed) - ONE
+    key part that all heads share -, both are rotated by the spec's position encoding, and the score is
+    (q_unrotated . W_uk c + q_rotated . k_rotated) * softmax_scale; the cache row is then [c | rotated key part].
+    ``gate`` false: no W_g and no gate.  ``spec.window`` = w: a token sees itself and the w - 1 tokens before it (the
+    cache gives the pages behind the window back while the request runs).
+
     Keys and values are never materialised.  Since q . (W_uk c) = (W_uk^T q) . c and sum_j p_j W_uv c_j =
     W_uv sum_j p_j c_j, each head's query is carried into the latent space, the attention runs over the
     latent pages as keys AND values - one shared "kv head" of size latent_rank, which is exactly what the
     paged attention kernels of this package take (plain, split-K decode, flash-style and tcgen05 prefill) -
-    and the result leaves through W_uv.  Projections of x (q | gate | dkv) are one product."""
+    and the result leaves through W_uv.  Projections of x (q | gate | dkv) are one product.  With a rotated part the
+    shared head is [c | key part], rank + n wide: the per-head matrix that carries the query over is W_uk^T with an
+    identity block behind it (the rotated dimensions pass through unchanged and are rotated afterwards, in the kernel
+    that writes the cache row), and W_uv has zero columns for the key part."""
 
     kernel_modules = ("latent",)       # libraries of csrc that this part's kernels live in
     kernel_modules_bf16 = ("attention_prefill_tc",)
@@ -245,37 +261,69 @@ class LatentAttention(PagedAttendMixin, Part):
         return spec.num_heads, spec.head_dim, int(e["value_dim"]), int(e["latent_rank"]), bool(e.get("own_latent", True))
 
     @staticmethod
+    def _options(spec):
+        e = spec.extra_dict()
+        return int(e.get("rope_dim", 0) or 0), bool(e.get("gate", True))
+
+    @staticmethod
     def weight_slots(spec, hidden_size: int) -> Dict[str, WeightSlot]:
         h, d, v, r, own = LatentAttention._dims(spec)
-        slots = {"q": WeightSlot((h * d, hidden_size))}
+        n, gate = LatentAttention._options(spec)
+        slots = {"q": WeightSlot((h * (d + n), hidden_size))}
         if own:
-            slots["dkv"] = WeightSlot((r, hidden_size))
+            slots["dkv"] = WeightSlot((r + n, hidden_size))
             slots["dkv.norm"] = WeightSlot((r,), init="ones")
-        slots.update({"uk": WeightSlot((h * d, r)), "uv": WeightSlot((h * v, r)), "g": WeightSlot((h, hidden_size)),
-                      "o": WeightSlot((hidden_size, h * v))})
+        slots.update({"uk": WeightSlot((h * d, r)), "uv": WeightSlot((h * v, r))})
+        if gate:
+            slots["g"] = WeightSlot((h, hidden_size))
+        slots["o"] = WeightSlot((hidden_size, h * v))
         return slots
 
     def __init__(self, spec, hidden_size, weights, rt) -> None:
         Part.__init__(self, spec, hidden_size, weights, rt)
         h, d, v, r, own = self._dims(spec)
-        if h <= 0 or d <= 0 or v <= 0 or not 0 < r <= 512:
-            raise ConfigError(f"latent attention: heads and sizes must be positive and the latent rank at most 512 (got {r})")
-        # what the attention kernels see: h query heads over one shared head of size r
-        self.n_heads, self.n_kv, self.head_dim = h, 1, r
+        n, gate = self._options(spec)
+        if h <= 0 or d <= 0 or v <= 0 or n < 0 or n % 2 or not 0 < r + n <= 512:
+            raise ConfigError(f"latent attention: heads and sizes must be positive, the rotated part even, and the latent "
+                              f"rank with it at most 512 (got {r} + {n})")
+        if spec.window is not None and spec.window <= 0:
+            raise ConfigError("an attention window must be positive")
+        # what the attention kernels see: h query heads over one shared head of size r (+ the rotated key part)
+        self.n_heads, self.n_kv, self.head_dim = h, 1, r + n
         self.qk_dim, self.value_dim, self.rank, self.own_latent = d, v, r, own
-        self.window = None
+        self.rope_dim, self.gated = n, gate
+        self.window = spec.window
         self.scale = float(spec.softmax_scale)
         self.eps = float(spec.extra_dict().get("norm_eps", 1e-6))
+        if n > 0:
+            self.rotation = part("position", spec.position.kind)(spec.position, hidden_size, {}, rt)
+            if self.rotation.rotary_dim != n or getattr(self.rotation, "head_slopes", None) is not None or \
+                    float(getattr(self.rotation, "magnitude", 1.0)) != 1.0:
+                raise ConfigError("latent attention: the position encoding must rotate exactly the rope_dim dimensions")
+        # the attention kernels themselves rotate nothing: what they see is already encoded
         self.position = part("position", "none")(spec.position, hidden_size, {}, rt)
-        rows = [weights["q"], weights["g"]] + ([weights["dkv"]] if own else [])
+        rows = [weights["q"]] + ([weights["g"]] if gate else []) + ([weights["dkv"]] if own else [])
+        self.latent_col = h * (d + n) + (h if gate else 0)
+        if n > 0:
+            pad = -sum(w.shape[0] for w in rows) % 8      # zero rows, so that every row of the result starts on 16 bytes
+            if pad:
+                rows.append(torch.zeros(pad, hidden_size, dtype=weights["q"].dtype, device=weights["q"].device))
         self.w_in = rt.weight(torch.cat(rows, dim=0))
         self.latent_gain = rt.gain(weights["dkv.norm"]) if own else None
-        self.w_uk_t = rt.weight(weights["uk"].view(h, d, r).transpose(1, 2))      # [h, r, d]: q -> latent space
-        self.w_uv = rt.weight(weights["uv"].view(h, v, r))                         # [h, v, r]: latent space -> values
+        uk_t = weights["uk"].view(h, d, r).transpose(1, 2)                         # [h, r, d]: q -> latent space
+        uv = weights["uv"].view(h, v, r)                                           # [h, v, r]: latent space -> values
+        if n > 0:
+            carry = torch.zeros(h, r + n, d + n, dtype=uk_t.dtype, device=uk_t.device)
+            carry[:, :r, :d] = uk_t
+            carry[:, r:, d:] = torch.eye(n, dtype=uk_t.dtype, device=uk_t.device)   # the rotated part passes through
+            uk_t = carry
+            uv = torch.cat([uv, torch.zeros(h, v, n, dtype=uv.dtype, device=uv.device)], dim=2)
+        self.w_uk_t = rt.weight(uk_t)
+        self.w_uv = rt.weight(uv)
         self.w_o = rt.weight(weights["o"])
 
     def cache_need(self):
-        return PagedNeed((("latent", (self.rank,)),), None) if self.own_latent else None
+        return PagedNeed((("latent", (self.rank + self.rope_dim,)),), self.window) if self.own_latent else None
 
     def weights_in_order(self) -> tuple:
         return (self.w_in, self.w_o)
@@ -295,20 +343,31 @@ class LatentAttention(PagedAttendMixin, Part):
     def finish(self, proj: torch.Tensor, ctx, cache, residual=None):
         rt = self.rt
         n = proj.shape[0]
-        h, d, v, r = self.n_heads, self.qk_dim, self.value_dim, self.rank
+        h, d, v, r, rope = self.n_heads, self.qk_dim, self.value_dim, self.rank, self.rope_dim
         table = ctx.block_tables[cache.group]
-        pages = cache.pages["latent"]                                  # [P, page_size, r]
-        if self.own_latent:
-            if not cache.writable:
-                raise ConfigError("latent attention: a layer with a latent of its own needs a cache of its own")
-            ops.latent_norm_write(proj, h * d + h, r, self.latent_gain, self.eps, pages, ctx.positions,
+        pages = cache.pages["latent"]                                  # [P, page_size, r + rope]
+        if self.own_latent and not cache.writable:
+            raise ConfigError("latent attention: a layer with a latent of its own needs a cache of its own")
+        if rope == 0 and self.own_latent:
+            ops.latent_norm_write(proj, self.latent_col, r, self.latent_gain, self.eps, pages, ctx.positions,
                                   ctx.seq_of_token, table, rt.page_size)
-        q_latent = rt.heads_linear(proj[:, :h * d], self.w_uk_t)       # [T, h r]
-        mixed = rt.empty(n, h * r)
-        as_kv = pages.view(pages.shape[0], 1, rt.page_size, r)
+        q_latent = rt.heads_linear(proj[:, :h * (d + rope)], self.w_uk_t)       # [T, h (r + rope)]
+        if rope > 0:
+            if not self.own_latent:
+                raise ConfigError("latent attention: a rotated key part needs a latent of the layer's own")
+            # the cache row [c | rotated key part], and the queries' last rope dimensions rotated in place
+            ops.latent_rope_write(proj, self.latent_col, r, rope, self.latent_gain, self.eps, pages, ctx.positions,
+                                  ctx.seq_of_token, table, rt.page_size, self.rotation.inv_freq, self.rotation.interleaved,
+                                  q_latent, h)
+        mixed = rt.empty(n, h * (r + rope))
+        as_kv = pages.view(pages.shape[0], 1, rt.page_size, r + rope)
         self._attend(q_latent, _KeyValuePages(as_kv, as_kv), mixed, ctx, table)
         out = rt.heads_linear(mixed, self.w_uv)                        # [T, h v]
-        ops.head_gate(out, proj, h * d, h, v)
+        if self.gated:
+            ops.head_gate(out, proj, h * (d + rope), h, v)
+        if rope > 0:
+            # the product leaves in FP32 (or is added into the FP32 stream by the kernel itself)
+            return rt.linear(out, self.w_o, out_dtype=torch.float32, residual=residual)
         return rt.linear(out, self.w_o, residual=residual)
 
 
@@ -424,7 +483,13 @@ class NormedQKAttention(PagedAttendMixin, Part):
         q, k <- the position encoding                           (rotary: pairs (i, i + rotary_dim / 2) of the first
                                                                 ``rotary_dim`` dimensions of every head; the encoding's
                                                                 ``magnitude`` multiplies cosine and sine)
+        q, k <- q, k / sqrt(mean over the head (q^2) + eps)     each head on its own, no weight (only with ``head_unit_norm``)
         s = (q . k) softmax_scale;  causal softmax;  sum p v;   then W_o on the heads side by side
+
+    More options in the spec's extra: ``chunk`` = c > 0 - a token at position p sees only the keys of its own chunk,
+    positions p - p % c .. p, chunks counted from the sequence's start; ``sink`` - one is added to the softmax's
+    denominator (a key of score 0 that has no value); ``head_gate`` - head h's output is multiplied by
+    sigmoid(W_g x)_h, one more row per head in the fused projection ("g").
 
     Keys have ``head_dim`` entries, values ``value_dim`` (the same unless the extra says otherwise).  The three
     projections are one product; bias, both norms, the rotation and the cache write are one kernel
@@ -453,6 +518,8 @@ class NormedQKAttention(PagedAttendMixin, Part):
             slots.update({"q.b": WeightSlot((h * d,)), "k.b": WeightSlot((g * d,)), "v.b": WeightSlot((g * v,))})
         if qk_norm:
             slots.update({"q.norm": WeightSlot((h * d,), init="ones"), "k.norm": WeightSlot((g * d,), init="ones")})
+        if spec.extra_dict().get("head_gate", False):
+            slots["g"] = WeightSlot((h, hidden_size))
         slots["o"] = WeightSlot((hidden_size, h * v))
         return slots
 
@@ -464,11 +531,18 @@ class NormedQKAttention(PagedAttendMixin, Part):
         if not 0 < d <= 512 or not 0 < v <= 512:
             raise ConfigError(f"normed-qk attention: key size {d} and value size {v} must lie in 1 .. 512")
         if spec.window is not None:
-            raise ConfigError("normed-qk attention sees every earlier key (no window)")
+            raise ConfigError("normed-qk attention sees every earlier key, or those of its chunk (no window)")
+        e = spec.extra_dict()
         self.n_heads, self.n_kv, self.head_dim, self.value_dim = h, g, d, v
         self.window = None
+        self.chunk, self.sink = int(e.get("chunk", 0) or 0), bool(e.get("sink", False))
+        self.head_unit_norm, self.head_gate = bool(e.get("head_unit_norm", False)), bool(e.get("head_gate", False))
+        if self.chunk < 0:
+            raise ConfigError("normed-qk attention: a chunk must be a positive number of tokens")
+        if self.head_gate:
+            self.kernel_modules = ("latent",)         # the library of csrc that holds the per-head gate
         self.scale = float(spec.softmax_scale)
-        self.eps = float(spec.extra_dict().get("norm_eps", 1e-6))
+        self.eps = float(e.get("norm_eps", 1e-6))
         self.position = part("position", spec.position.kind)(spec.position, hidden_size, {}, rt)
         if self.position.rotary_dim > d or (self.position.rotary_dim > 0 and self.position.interleaved):
             raise ConfigError("normed-qk attention rotates the pairs (i, i + rotary_dim / 2) of at most head_dim dimensions")
@@ -477,9 +551,9 @@ class NormedQKAttention(PagedAttendMixin, Part):
         self.magnitude = float(getattr(self.position, "magnitude", 1.0))
         self.inv_freq = self.position.inv_freq if self.position.rotary_dim > 0 else \
             torch.zeros(0, dtype=torch.float32, device=rt.device)
-        self.cols = (h + g) * d + g * v
-        rows = [weights["q"], weights["k"], weights["v"]]
-        pad = -self.cols % 8                      # zero rows, so that every row of the result starts on 16 bytes
+        self.cols = (h + g) * d + g * v               # the gates' columns follow these
+        rows = [weights["q"], weights["k"], weights["v"]] + ([weights["g"]] if self.head_gate else [])
+        pad = -(self.cols + (h if self.head_gate else 0)) % 8     # zero rows, so that every row of the result starts on 16 bytes
         if pad:
             rows.append(torch.zeros(pad, hidden_size, dtype=weights["q"].dtype, device=weights["q"].device))
         self.w_qkv = rt.weight(torch.cat(rows, dim=0))
@@ -489,6 +563,8 @@ class NormedQKAttention(PagedAttendMixin, Part):
         self.k_gain = rt.gain(weights["k.norm"]) if qk_norm else None
 
     def cache_need(self):
+        # (a chunked mask keeps all pages: keys before the running chunk are never read again, but nothing gives
+        # them back before the request ends)
         if self.value_dim == self.head_dim:
             return PagedKVNeed(self.n_kv, self.head_dim, None)
         return PagedNeed((("k", (self.n_kv, self.head_dim)), ("v", (self.n_kv, self.value_dim))), None)
@@ -519,16 +595,76 @@ class NormedQKAttention(PagedAttendMixin, Part):
         q = rt.empty(n, h * d)
         ops.qk_norm_rope(qkv, self.bias, self.q_gain, self.k_gain, self.eps, ctx.positions, ctx.seq_of_token, table,
                          self.inv_freq, self.magnitude, q, cache.k_pages if cache.writable else None,
-                         cache.v_pages if cache.writable else None, h, g, d, v, self.position.rotary_dim, rt.page_size)
+                         cache.v_pages if cache.writable else None, h, g, d, v, self.position.rotary_dim, rt.page_size,
+                         head_unit=self.head_unit_norm)
         att = rt.empty(n, h * v)
         if v == d:
             self._attend(q, cache, att, ctx, table)
         else:
             ops.attention_generic(q, cache.k_pages, cache.v_pages, att, ctx.positions, ctx.seq_of_token, table,
-                                  h, g, d, rt.page_size, None, self.scale, value_dim=v)
+                                  h, g, d, rt.page_size, None, self.scale, value_dim=v, chunk=self.chunk, sink=self.sink)
+        if self.head_gate:
+            ops.head_gate(att, qkv, self.cols, h, v)
         # the product leaves in FP32 (or is added into the FP32 stream by the kernel itself): the residual sum
         # sees it unrounded
         return rt.linear(att, self.w_o, out_dtype=torch.float32, residual=residual)
+
+
+class ParallelMixers(Part):
+    """Two mixers side by side that read the same input: y = left_scale * left(x) + right_scale * right(x).  The two
+    specs (``left``, ``right``: MixerSpec of any registered kinds) and the two scales come in the spec's extra; the
+    weights of each lie under its side's name ("left.q", "right.o", ...).  Each side keeps what it needs between steps
+    in the layer run's one cache view - so at most one of them may need pages, and at most one a state (attention beside
+    a recurrence, say).  The sum is FP32."""
+
+    kernel_modules = ("pointwise",)       # the library of csrc that holds the weighted sum
+
+    adds_into_residual = False
+
+    @staticmethod
+    def _sides(spec):
+        e = spec.extra_dict()
+        return (("left", e["left"], float(e.get("left_scale", 1.0))), ("right", e["right"], float(e.get("right_scale", 1.0))))
+
+    @staticmethod
+    def weight_slots(spec, hidden_size: int) -> Dict[str, WeightSlot]:
+        slots = {}
+        for name, sub, _ in ParallelMixers._sides(spec):
+            for slot, ws in part("mixer", sub.kind).weight_slots(sub, hidden_size).items():
+                slots[f"{name}.{slot}"] = ws
+        return slots
+
+    def __init__(self, spec, hidden_size, weights, rt) -> None:
+        Part.__init__(self, spec, hidden_size, weights, rt)
+        self.sub_parts, self.scales = [], []
+        for name, sub, scale in self._sides(spec):
+            own = {slot[len(name) + 1:]: w for slot, w in weights.items() if slot.startswith(name + ".")}
+            self.sub_parts.append(part("mixer", sub.kind)(sub, hidden_size, own, rt))
+            self.scales.append(scale)
+        safety = [getattr(p, "graph_safe", "none") for p in self.sub_parts]
+        self.graph_safe = "all" if all(x == "all" for x in safety) else \
+            ("decode" if all(x in ("decode", "all") for x in safety) else "none")
+
+    def cache_need(self):
+        needs = []
+        for p in self.sub_parts:
+            need = p.cache_need()
+            needs += list(need) if isinstance(need, tuple) else ([need] if need is not None else [])
+        paged = [x for x in needs if isinstance(x, (PagedKVNeed, PagedNeed))]
+        states = [x for x in needs if isinstance(x, StateNeed)]
+        if len(paged) > 1 or len(states) > 1:
+            raise ConfigError("mixers side by side: at most one of them may keep pages, and at most one a state")
+        return tuple(needs) if len(needs) > 1 else (needs[0] if needs else None)
+
+    def weights_in_order(self) -> tuple:
+        return tuple(w for p in self.sub_parts for w in getattr(p, "weights_in_order", tuple)())
+
+    def forward(self, x: torch.Tensor, ctx, cache):
+        left, right = (p.forward(x, ctx, cache) for p in self.sub_parts)
+        if left.dtype != torch.float32 or right.dtype != torch.float32:
+            raise ConfigError("mixers side by side must hand their outputs over in FP32")
+        ops.weighted_sum(left, self.scales[0], right, self.scales[1], left)
+        return left
 
 
 def _pairs_adjacent(w: torch.Tensor, n_heads: int, head_dim: int, rotary_dim: int) -> torch.Tensor:
@@ -543,3 +679,4 @@ register_part("mixer", "attention", PagedAttention, replace=True)
 register_part("mixer", "latent_attention", LatentAttention, replace=True)
 register_part("mixer", "conv_key_attention", ConvKeyAttention, replace=True)
 register_part("mixer", "normed_qk_attention", NormedQKAttention, replace=True)
+register_part("mixer", "parallel_mixers", ParallelMixers, replace=True)

@@ -50,5 +50,20 @@ class ScalarRMSNorm(RMSNorm):
         self.gain = rt.gain(weights["weight"]).reshape(1).expand(hidden_size).contiguous()
 
 
+class RMSNormOnePlus(RMSNorm):
+    """y = x * rsqrt(mean(x^2) + eps) * (1 + w): the weight is stored around zero.  On the device the gain is 1 + w in
+    FP32, so every kernel that takes an RMSNorm - the fused ones included - takes this one unchanged."""
+
+    @staticmethod
+    def weight_slots(spec, hidden_size: int) -> Dict[str, WeightSlot]:
+        return {"weight": WeightSlot((hidden_size,), init="zeros")}
+
+    def __init__(self, spec, hidden_size, weights, rt) -> None:
+        Part.__init__(self, spec, hidden_size, weights, rt)
+        self.eps = float(spec.eps)
+        self.gain = rt.gain(weights["weight"]) + 1.0
+
+
 register_part("norm", "rmsnorm", RMSNorm, replace=True)
+register_part("norm", "rmsnorm_one_plus", RMSNormOnePlus, replace=True)
 register_part("norm", "rmsnorm_scalar", ScalarRMSNorm, replace=True)

@@ -126,6 +126,51 @@ def yarn_frequencies(rotary_dim: int, theta: float, scaling):
     return freq / factor * ramp + freq * (1.0 - ramp), 0.1 * math.log(factor) + 1.0
 
 
+class RotaryEncodingScaled(RotaryEncoding):
+    """Rotary encoding with f_i = theta^(-2i / n) (n = rotary_dim) and one of two rescaling rules, or none:
+
+        "linear"   every f_i is divided by ``factor``;
+        "llama3"   by wavelength l = 2 pi / f: l < original / high keeps f; l > original / low gives f / factor; between
+                   the two, with s = (original / l - low) / (high - low), (1 - s) f / factor + s f.
+
+    Unlike ``RotaryEncoding`` (which follows the reference's FP32 arithmetic step by step) the frequencies are computed
+    in double precision and rounded once to FP32; angles stay FP32 products position * frequency on the device."""
+
+    def __init__(self, spec, hidden_size, weights, rt) -> None:
+        Part.__init__(self, spec, hidden_size, weights, rt)
+        n = spec.rotary_dim
+        if n <= 0 or n % 2:
+            raise ConfigError(f"rotary_dim {n} must be positive and even")
+        if spec.pairing not in ("half", "interleaved"):
+            raise ConfigError(f"rope pairing '{spec.pairing}' must be 'half' or 'interleaved'")
+        self.rotary_dim = n
+        self.interleaved = spec.pairing == "interleaved"
+        self.inv_freq = torch.from_numpy(scaled_frequencies(n, spec.theta, spec.scaling).astype(np.float32)).to(rt.device)
+
+
+def scaled_frequencies(rotary_dim: int, theta: float, scaling) -> np.ndarray:
+    """float64 frequencies [rotary_dim / 2] of RotaryEncodingScaled."""
+    i = np.arange(rotary_dim // 2, dtype=np.float64)
+    freq = np.power(float(theta), -2.0 * i / rotary_dim)
+    if scaling is None:
+        return freq
+    factor = float(scaling.factor)
+    if factor <= 0:
+        raise ConfigError("rope scaling: the factor must be positive")
+    if scaling.rope_type == "linear":
+        return freq / factor
+    if scaling.rope_type == "llama3":
+        original = float(scaling.original_max_position_embeddings)
+        low, high = float(scaling.low_freq_factor), float(scaling.high_freq_factor)
+        if original <= 0 or low <= 0 or high <= low:
+            raise ConfigError("rope scaling: original and low must be positive and high above low")
+        wavelength = 2.0 * math.pi / freq
+        s = (original / wavelength - low) / (high - low)
+        blend = (1.0 - s) * freq / factor + s * freq
+        return np.where(wavelength < original / high, freq, np.where(wavelength > original / low, freq / factor, blend))
+    raise ConfigError(f"rope scaling '{scaling.rope_type}' is not one of linear, llama3")
+
+
 class NoEncoding(Part):
     """No position encoding: queries and keys are used as projected."""
     head_slopes = None
@@ -141,4 +186,5 @@ class NoEncoding(Part):
 register_part("position", "rope", RotaryEncoding, replace=True)
 register_part("position", "rope_exact", RotaryEncodingExact, replace=True)
 register_part("position", "rope_yarn", RotaryEncodingYarn, replace=True)
+register_part("position", "rope_scaled", RotaryEncodingScaled, replace=True)
 register_part("position", "none", NoEncoding, replace=True)

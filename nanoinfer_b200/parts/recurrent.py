@@ -6,7 +6,7 @@ from typing import Dict
 import torch
 
 from ..config.model_config import ConfigError
-from ..config.registry import register_part
+from ..config.registry import part, register_part
 from ..kernels import ops
 from .base import Part, StateNeed, WeightSlot
 
@@ -191,5 +191,95 @@ class LightningAttention(Part):
         return rt.linear(y, self.w_o, out_dtype=torch.float32, residual=residual)
 
 
+class Retention(Part):
+    """Retention: linear attention with a fixed decay per head, rotated queries and keys, no softmax and no
+    denominator.  Per head, with a matrix state S [head_dim, value_dim] in FP32 that starts at zero and is carried from
+    token to token for each request:
+
+        q = rot(W_q x), k = rot(W_k x) * key_scale  (head_dim entries), v = W_v x  (value_dim entries)
+        S <- decay_head * S + k v^T;   o = S^T q
+
+    rot is the spec's position encoding (pairs (i, i + rotary_dim / 2) of the first ``rotary_dim`` dimensions of every
+    head).  Each head's o is divided by its own root mean square (``norm_eps``, no weight); the heads side by side are
+    multiplied by silu(W_g x) and leave through W_o.  ``decay`` (one number per head), ``value_dim`` and ``key_scale``
+    (head_dim^-1/2 unless given) come in the spec's extra.
+
+    The four projections of x are ONE product (rows q | k | v | gate).  Rotation and key scale give q, k, v in FP32
+    (one kernel); from there the recurrence is the one of lightning attention without its activations
+    (csrc/lightning.cu: chunk sums, scan and read-outs for prompt portions, one launch for single tokens), on the FP32
+    numbers, so that rotated queries and keys are never rounded to the activations' type; the state is a slot of the
+    runner's state pool."""
+
+    kernel_modules = ("lightning",)       # libraries of csrc that this part's kernels live in
+
+    adds_into_residual = True
+    graph_safe = "all"
+
+    @staticmethod
+    def _dims(spec):
+        e = spec.extra_dict()
+        return spec.num_heads, spec.head_dim, int(e.get("value_dim", spec.head_dim))
+
+    @staticmethod
+    def weight_slots(spec, hidden_size: int) -> Dict[str, WeightSlot]:
+        h, d, v = Retention._dims(spec)
+        return {"q": WeightSlot((h * d, hidden_size)), "k": WeightSlot((h * d, hidden_size)),
+                "v": WeightSlot((h * v, hidden_size)), "g": WeightSlot((h * v, hidden_size)),
+                "o": WeightSlot((hidden_size, h * v))}
+
+    def __init__(self, spec, hidden_size, weights, rt) -> None:
+        super().__init__(spec, hidden_size, weights, rt)
+        h, d, v = self._dims(spec)
+        e = spec.extra_dict()
+        decay = tuple(float(x) for x in e.get("decay", ()))
+        if h <= 0 or v <= 0 or len(decay) != h:
+            raise ConfigError("retention: heads and value size must be positive, with one decay per head")
+        if not 0 < d <= ops.LIGHTNING_MAX_DIM:
+            raise ConfigError(f"retention: a key size of {d} is not supported (1 to {ops.LIGHTNING_MAX_DIM})")
+        self.H, self.D, self.V = h, d, v
+        self.eps = float(e.get("norm_eps", 1e-6))
+        self.key_scale = float(e["key_scale"]) if e.get("key_scale") is not None else float(d) ** -0.5
+        self.position = part("position", spec.position.kind)(spec.position, hidden_size, {}, rt)
+        if self.position.rotary_dim > d or (self.position.rotary_dim > 0 and self.position.interleaved) or \
+                getattr(self.position, "head_slopes", None) is not None or float(getattr(self.position, "magnitude", 1.0)) != 1.0:
+            raise ConfigError("retention rotates the pairs (i, i + rotary_dim / 2) of at most head_dim dimensions")
+        rows = [weights[s] for s in ("q", "k", "v", "g")]
+        self.gate_col = 2 * h * d + h * v
+        pad = -(self.gate_col + h * v) % 8         # zero rows, so that every row of the result starts on 16 bytes
+        if pad:
+            rows.append(torch.zeros(pad, hidden_size, dtype=weights["q"].dtype, device=weights["q"].device))
+        self.w_in = rt.weight(torch.cat(rows, dim=0))
+        self.w_o = rt.weight(weights["o"])
+        self.decay = torch.tensor(decay, dtype=torch.float32, device=rt.device)
+
+    def cache_need(self):
+        return StateNeed((self.H * self.D * self.V,), "float32")
+
+    def weights_in_order(self) -> tuple:
+        return (self.w_in, self.w_o)
+
+    def forward(self, x: torch.Tensor, ctx, cache, residual=None):
+        return self.finish(self.rt.linear(x, self.w_in), ctx, cache, residual=residual)
+
+    def finish(self, proj: torch.Tensor, ctx, cache, residual=None):
+        rt = self.rt
+        n = proj.shape[0]
+        h, d, v = self.H, self.D, self.V
+        f32 = torch.float32
+        qkv = rt.empty(n, self.gate_col, dtype=f32)
+        ops.linear_attention_prepare(proj, ctx.positions, self.position.inv_freq, self.key_scale, qkv, h, d, v,
+                                     self.position.rotary_dim)
+        o = rt.empty(n, h * v, dtype=f32)
+        buf = None
+        if ctx.max_q_len > 1:       # chunks: every chunk's own sum, then the state before it (one buffer for all layers)
+            buf = rt.workspace("lightning_chunks", ops.lightning_max_chunks(n, ctx.n_seqs) * h * d * v, f32)
+        ops.lightning_recurrence(qkv, cache.state, ctx.cu_q, ctx.slots, ctx.n_seqs, self.decay, h, d, v, o,
+                                 max_q_len=ctx.max_q_len, buf=buf, activation=False)
+        y = rt.empty(n, h * v)
+        ops.group_gated_norm(o, proj, self.gate_col, None, self.eps, y, v, gate="silu")
+        return rt.linear(y, self.w_o, out_dtype=f32, residual=residual)
+
+
 register_part("mixer", "gated_delta", GatedDeltaRule, replace=True)
+register_part("mixer", "retention", Retention, replace=True)
 register_part("mixer", "lightning", LightningAttention, replace=True)

@@ -35,7 +35,10 @@ def tensor_plan(config: ModelConfig) -> List[PlannedTensor]:
 
     emb = config.embedding_spec()
     add(("embedding",), registry.part("embedding", emb.kind).weight_slots(emb, d))
+    used = {run.layer for run in config.schedule}
     for i, layer in enumerate(config.layers):
+        if i not in used:                                     # runs with another layer's weights: no tensors of its own
+            continue
         add(("layer", i, "mixer_norm"),
             registry.part("norm", layer.mixer_norm.kind).weight_slots(layer.mixer_norm, d))
         add(("layer", i, "mixer"),
