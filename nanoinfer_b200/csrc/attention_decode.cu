@@ -108,6 +108,8 @@ __device__ __forceinline__ void dec_warm(const unsigned char* p, unsigned long l
 // every split writes its partial result into the shared memory of the cluster's first block, one
 // cluster barrier, and that block merges them in split order - no scratch in global memory, no
 // fence, no ticket.
+// chunk > 0: the token at position p sees only the keys from p - p % chunk on; sink: one is added to the softmax's
+// denominator.
 // CAP: the scaled scores are bounded smoothly, s <- cap * tanh(s / cap), before the softmax.  The kernel is then
 // handed scale_log2e = 2 log2(e) scale / cap and cap_l2 = cap log2(e): with x = exp2(raw * scale_log2e),
 // cap_l2 - 2 cap_l2 / (x + 1) is the capped score in the exponent's base.
@@ -120,7 +122,7 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
                         int bt_stride, int n_q_heads, int n_kv_heads, int page_size, int window,
                         float scale_log2e, float cap_l2, int n_splits, float* __restrict__ scratch,
                         int* __restrict__ tickets, const unsigned char* __restrict__ warm_a, unsigned long long warm_a_bytes,
-                        const unsigned char* __restrict__ warm_b, unsigned long long warm_b_bytes) {
+                        const unsigned char* __restrict__ warm_b, unsigned long long warm_b_bytes, int chunk, int sink) {
     // Weights that the kernels after this one will read (the caller's hint, up to two regions): asked
     // into L2 now, in pieces dealt over the blocks, while this kernel - which waits on latencies
     // more than on bandwidth - leaves the memory system room.  Nothing here depends on the kernel before.
@@ -143,7 +145,8 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
     const int pos = positions[t_idx];
     const int* table = block_table + (size_t)seq_of_token[t_idx] * bt_stride;
     const int G = n_q_heads / n_kv_heads;
-    const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+    int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+    if (chunk > 0 && pos - pos % chunk > lo) lo = pos - pos % chunk;      // only the keys of the token's own chunk
     const int n_keys = pos + 1 - lo;
     // the split's key range, in whole 64-key chunks
     const int chunks_total = (n_keys + 63) / 64;
@@ -159,6 +162,12 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
 #pragma unroll
     for (int j = 0; j < NT_O; ++j) o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f;
     float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;   // rows g and g + 8
+    if (sink && split == 0 && warp == 0) {
+        // one more term in every row's denominator: a key of score 0 without a value, counted once - by the first
+        // warp of the first split (which always has the token's own key), in one lane of each row's four
+        m0 = m1 = 0.f;
+        if (t == 0) l0 = l1 = 1.f;
+    }
     uint32_t qa[KS][4];
 
     // Asks for the keys and values of segment [seg0, seg0 + SEG) into buffer `buf`.  The last
@@ -822,7 +831,7 @@ static int launch_decode_cl(const void* q, const void* k_pages, const void* v_pa
                          int bt_stride, int n_q_heads, int n_kv_heads, int page_size, int window,
                          float scale_log2e, float cap_l2, int n_splits, float* scratch, int* tickets, const void* warm_a,
                          unsigned long long warm_a_bytes, const void* warm_b, unsigned long long warm_b_bytes,
-                         cudaStream_t stream) {
+                         int chunk, int sink, cudaStream_t stream) {
     const size_t kv_smem = (size_t)(16 + 4 * SEG) * HD * sizeof(__nv_bfloat16);
     const size_t smem = kv_smem + (CL ? (size_t)n_splits * (n_q_heads / n_kv_heads) * (HD + 2) * sizeof(float) : 0);
     static size_t configured = 0;
@@ -859,7 +868,7 @@ static int launch_decode_cl(const void* q, const void* k_pages, const void* v_pa
                                        (__nv_bfloat16*)out, token_list, positions, seq_of_token, block_table,
                                        bt_stride, n_q_heads, n_kv_heads, page_size, window, scale_log2e, cap_l2, n_splits,
                                        scratch, tickets, (const unsigned char*)warm_a, warm_a_bytes,
-                                       (const unsigned char*)warm_b, warm_b_bytes);
+                                       (const unsigned char*)warm_b, warm_b_bytes, chunk, sink);
     return e == cudaSuccess ? NI_OK : (int)e;
 }
 
@@ -877,14 +886,14 @@ static int launch_decode(const void* q, const void* k_pages, const void* v_pages
                          int bt_stride, int n_q_heads, int n_kv_heads, int page_size, int window,
                          float scale_log2e, float cap_l2, int n_splits, float* scratch, int* tickets, const void* warm_a,
                          unsigned long long warm_a_bytes, const void* warm_b, unsigned long long warm_b_bytes,
-                         cudaStream_t stream) {
+                         int chunk, int sink, cudaStream_t stream) {
     const size_t slot_bytes = (size_t)n_splits * (n_q_heads / n_kv_heads) * (HD + 2) * sizeof(float);
     const bool few_blocks = (long long)n_items * n_kv_heads * n_splits <= 2LL * ni_sm_count() && slot_bytes <= 65536;
     if (dec_cluster_merge && n_splits >= 2 && ((n_splits <= 8 && slot_bytes <= DEC_CLUSTER_SLOT_BYTES) || (n_splits <= 16 && few_blocks)))
 #define NI_DEC_GO(CL, CAP)                                                                                          \
     launch_decode_cl<HD, SEG, CL, CAP>(q, k_pages, v_pages, out, token_list, n_items, positions, seq_of_token,          \
                                        block_table, bt_stride, n_q_heads, n_kv_heads, page_size, window, scale_log2e,   \
-                                       cap_l2, n_splits, scratch, tickets, warm_a, warm_a_bytes, warm_b, warm_b_bytes, stream)
+                                       cap_l2, n_splits, scratch, tickets, warm_a, warm_a_bytes, warm_b, warm_b_bytes, chunk, sink, stream)
         return cap_l2 > 0.f ? NI_DEC_GO(true, true) : NI_DEC_GO(true, false);
     return cap_l2 > 0.f ? NI_DEC_GO(false, true) : NI_DEC_GO(false, false);
 #undef NI_DEC_GO
@@ -900,8 +909,9 @@ static int decode_dispatch(const void* q, const void* k_pages, const void* v_pag
                                   int n_q_heads, int n_kv_heads, int head_dim, int page_size, int window,
                                   float scale, float score_cap, int n_splits, float* scratch, int* tickets,
                                   const void* warm_a, long long warm_a_bytes, const void* warm_b,
-                                  long long warm_b_bytes, cudaStream_t stream) {
+                                  long long warm_b_bytes, int chunk, int sink, cudaStream_t stream) {
     if (n_items <= 0) return NI_OK;
+    if (chunk < 0) return NI_ERR_BAD_ARGUMENT;
     if (warm_a_bytes < 0 || (warm_a_bytes & 15) || (warm_a_bytes && (!warm_a || ((uintptr_t)warm_a & 15)))) return NI_ERR_BAD_ARGUMENT;
     if (warm_b_bytes < 0 || (warm_b_bytes & 15) || (warm_b_bytes && (!warm_b || ((uintptr_t)warm_b & 15)))) return NI_ERR_BAD_ARGUMENT;
     if (n_q_heads <= 0 || n_kv_heads <= 0 || n_q_heads % n_kv_heads || page_size <= 0 || n_splits <= 0 ||
@@ -920,16 +930,16 @@ static int decode_dispatch(const void* q, const void* k_pages, const void* v_pag
                 return launch_decode<64, 128>(q, k_pages, v_pages, out, token_list, n_items, positions, seq_of_token,
                                               block_table, bt_stride, n_q_heads, n_kv_heads, page_size, window,
                                               scale_log2e, cap_l2, n_splits, scratch, tickets, warm_a, (unsigned long long)warm_a_bytes, warm_b,
-                                              (unsigned long long)warm_b_bytes, stream);
+                                              (unsigned long long)warm_b_bytes, chunk, sink, stream);
             return launch_decode<64, 64>(q, k_pages, v_pages, out, token_list, n_items, positions, seq_of_token,
                                           block_table, bt_stride, n_q_heads, n_kv_heads, page_size, window,
                                           scale_log2e, cap_l2, n_splits, scratch, tickets, warm_a, (unsigned long long)warm_a_bytes, warm_b,
-                                              (unsigned long long)warm_b_bytes, stream);
+                                              (unsigned long long)warm_b_bytes, chunk, sink, stream);
         case 128:
             return launch_decode<128, 64>(q, k_pages, v_pages, out, token_list, n_items, positions, seq_of_token,
                                            block_table, bt_stride, n_q_heads, n_kv_heads, page_size, window,
                                            scale_log2e, cap_l2, n_splits, scratch, tickets, warm_a, (unsigned long long)warm_a_bytes, warm_b,
-                                              (unsigned long long)warm_b_bytes, stream);
+                                              (unsigned long long)warm_b_bytes, chunk, sink, stream);
         default: return NI_ERR_UNSUPPORTED_SIZE;
     }
 }
@@ -943,7 +953,22 @@ NI_EXPORT int ni_attention_decode(const void* q, const void* k_pages, const void
                                   long long warm_b_bytes, cudaStream_t stream) {
     return decode_dispatch(q, k_pages, v_pages, out, token_list, n_items, positions, seq_of_token, block_table, bt_stride,
                            n_q_heads, n_kv_heads, head_dim, page_size, window, scale, 0.f, n_splits, scratch, tickets,
-                           warm_a, warm_a_bytes, warm_b, warm_b_bytes, stream);
+                           warm_a, warm_a_bytes, warm_b, warm_b_bytes, 0, 0, stream);
+}
+
+// The same with a chunk mask (chunk > 0: the token at position p sees only the keys from p - p % chunk on) and, with
+// sink != 0, one added to the softmax's denominator; score_cap 0: scores are not bounded.
+NI_EXPORT int ni_attention_decode_masked(const void* q, const void* k_pages, const void* v_pages, void* out,
+                                         const int* token_list, int n_items, const int* positions,
+                                         const int* seq_of_token, const int* block_table, int bt_stride,
+                                         int n_q_heads, int n_kv_heads, int head_dim, int page_size, int window,
+                                         float scale, float score_cap, int chunk, int sink, int n_splits, float* scratch,
+                                         int* tickets, const void* warm_a, long long warm_a_bytes, const void* warm_b,
+                                         long long warm_b_bytes, cudaStream_t stream) {
+    if (score_cap < 0.f) return NI_ERR_BAD_ARGUMENT;
+    return decode_dispatch(q, k_pages, v_pages, out, token_list, n_items, positions, seq_of_token, block_table, bt_stride,
+                           n_q_heads, n_kv_heads, head_dim, page_size, window, scale, score_cap, n_splits, scratch, tickets,
+                           warm_a, warm_a_bytes, warm_b, warm_b_bytes, chunk, sink != 0, stream);
 }
 
 // The same with the scaled scores bounded by score_cap * tanh(s / score_cap) (score_cap > 0).
@@ -957,7 +982,7 @@ NI_EXPORT int ni_attention_decode_capped(const void* q, const void* k_pages, con
     if (!(score_cap > 0.f)) return NI_ERR_BAD_ARGUMENT;
     return decode_dispatch(q, k_pages, v_pages, out, token_list, n_items, positions, seq_of_token, block_table, bt_stride,
                            n_q_heads, n_kv_heads, head_dim, page_size, window, scale, score_cap, n_splits, scratch, tickets,
-                           warm_a, warm_a_bytes, warm_b, warm_b_bytes, stream);
+                           warm_a, warm_a_bytes, warm_b, warm_b_bytes, 0, 0, stream);
 }
 
 // ---- the variant that allocates nothing (see attention_decode_noalloc.h) ----------------------

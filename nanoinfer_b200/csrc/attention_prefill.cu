@@ -58,6 +58,8 @@ template <int HD> __device__ __forceinline__ int sw(int row, int chunk) {
     return row * HD + ((chunk ^ (row & MASK)) << 3);
 }
 
+// chunk > 0: a query at position p sees only the keys of its own chunk, p - p % chunk .. p (chunks counted from the
+// sequence's position 0).  sink: one is added to every row's softmax denominator (a key of score 0 without a value).
 // CAP: the scaled scores are bounded smoothly, s <- cap * tanh(s / cap), before mask and softmax.  The kernel is
 // then handed scale_log2e = 2 log2(e) scale / cap and cap_l2 = cap log2(e): with x = exp2(raw * scale_log2e),
 // cap_l2 * tanh(.) = cap_l2 - 2 cap_l2 / (x + 1) is the capped score in the exponent's base; its error is a few
@@ -69,7 +71,8 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat1
                          const int* __restrict__ tile_seq, const int* __restrict__ tile_row0,
                          const int* __restrict__ cu_q, const int* __restrict__ kv_len,
                          const int* __restrict__ block_table, int bt_stride, int n_q_heads,
-                         int n_kv_heads, int page_size, int window, float scale_log2e, float cap_l2) {
+                         int n_kv_heads, int page_size, int window, float scale_log2e, float cap_l2, int chunk,
+                         int sink) {
     constexpr int CH = HD / 8;        // 16-byte chunks per row
     constexpr int KS = HD / 16;       // k-steps over the head size
     constexpr int NT_O = HD / 8;      // output column tiles
@@ -99,10 +102,10 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat1
     const int last_pos = pos0 + row0 + rows - 1;
     int key_lo = 0;
     if (window > 0) key_lo = max(0, pos0 + row0 - window + 1);
+    if (chunk > 0) key_lo = max(key_lo, pos0 + row0 - (pos0 + row0) % chunk);      // the first row's chunk starts first
+    const int key_first = key_lo;                 // keys before it may lie in pages that were already given back
     key_lo = (key_lo / PF_BN) * PF_BN;
     const int n_tiles = (last_pos + 1 - key_lo + PF_BN - 1) / PF_BN;
-    // keys before the first row's window may lie in pages that were already given back
-    const int key_first = window > 0 ? max(0, pos0 + row0 - window + 1) : 0;
 
     // ---- load Q tile (rows beyond the portion: zeros) ----
     for (int idx = threadIdx.x; idx < PF_BM * CH; idx += blockDim.x) {
@@ -138,6 +141,7 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat1
     uint32_t qa[KS][4];
     const int qrow_a = pos0 + row0 + warp * 16 + g;   // position of this thread's rows g and g + 8
     const int qrow_b = qrow_a + 8;
+    const int chunk_a = chunk > 0 ? qrow_a - qrow_a % chunk : 0, chunk_b = chunk > 0 ? qrow_b - qrow_b % chunk : 0;
 
     for (int tile = 0; tile < n_tiles; ++tile) {
         const int stage = tile & 1;
@@ -156,7 +160,8 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat1
         // whole tile beyond this warp's rows (causal) or before their windows: nothing to add
         const int warp_last = pos0 + row0 + warp * 16 + 15;
         const int warp_first = pos0 + row0 + warp * 16;
-        const bool skip = k0 > warp_last || (window > 0 && k0 + PF_BN - 1 < warp_first - window + 1);
+        const bool skip = k0 > warp_last || (window > 0 && k0 + PF_BN - 1 < warp_first - window + 1) ||
+                          (chunk > 0 && k0 + PF_BN - 1 < warp_first - warp_first % chunk);
         if (!skip) {
             float s[PF_BN / 8][4];
 #pragma unroll
@@ -183,7 +188,8 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat1
             const float sl = CAP ? 1.0f : scale_log2e;     // capped scores are in the exponent's base already
             // Scores stay unscaled; the scale rides in the exponent's FMA: p = 2^(s * scale - m).
             // Only tiles that touch the diagonal or a window's edge need the mask.
-            const bool need_mask = k0 + PF_BN - 1 > warp_first || (window > 0 && k0 < warp_last - window + 1);
+            const bool need_mask = k0 + PF_BN - 1 > warp_first || (window > 0 && k0 < warp_last - window + 1) ||
+                                   (chunk > 0 && k0 < warp_last - warp_last % chunk);
             if (need_mask) {
 #pragma unroll
                 for (int j = 0; j < PF_BN / 8; ++j) {
@@ -193,6 +199,7 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat1
                         const int qp = (e < 2) ? qrow_a : qrow_b;
                         bool ok = key <= qp;
                         if (window > 0) ok = ok && key > qp - window;
+                        if (chunk > 0) ok = ok && key >= ((e < 2) ? chunk_a : chunk_b);
                         if (!ok) s[j][e] = -INFINITY;
                     }
                 }
@@ -251,6 +258,10 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat1
     cp_async_wait<0>();
     l0 += __shfl_xor_sync(0xffffffffu, l0, 1); l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
     l1 += __shfl_xor_sync(0xffffffffu, l1, 1); l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+    if (sink) {        // a key of score 0: its weight relative to the row's maximum (0 is the reference of a row without keys)
+        l0 += pf_exp2(-(m0 == -INFINITY ? 0.f : m0));
+        l1 += pf_exp2(-(m1 == -INFINITY ? 0.f : m1));
+    }
     const float inv0 = l0 > 0.f ? 1.f / l0 : 0.f, inv1 = l1 > 0.f ? 1.f / l1 : 0.f;
     const int ra = row0 + warp * 16 + g, rb = ra + 8;
 #pragma unroll
@@ -271,7 +282,8 @@ template <int HD, bool CAP> static int launch_prefill(const void* q, const void*
                                             const int* tile_seq, const int* tile_row0, int n_tiles,
                                             const int* cu_q, const int* kv_len, const int* block_table,
                                             int bt_stride, int n_q_heads, int n_kv_heads, int page_size,
-                                            int window, float scale_log2e, float cap_l2, cudaStream_t stream) {
+                                            int window, float scale_log2e, float cap_l2, int chunk, int sink,
+                                            cudaStream_t stream) {
     const size_t smem = (size_t)(PF_BM + 4 * PF_BN) * HD * sizeof(__nv_bfloat16);
     static bool configured = false;
     if (!configured) {
@@ -286,7 +298,7 @@ template <int HD, bool CAP> static int launch_prefill(const void* q, const void*
     attention_prefill_kernel<HD, CAP><<<grid, PF_WARPS * 32, smem, stream>>>(
         (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_pages, (const __nv_bfloat16*)v_pages,
         (__nv_bfloat16*)out, tile_seq, tile_row0, cu_q, kv_len, block_table, bt_stride, n_q_heads,
-        n_kv_heads, page_size, window, scale_log2e, cap_l2);
+        n_kv_heads, page_size, window, scale_log2e, cap_l2, chunk, sink);
     NI_RETURN_LAUNCH_STATUS();
 }
 
@@ -296,18 +308,18 @@ NI_EXPORT int ni_attention_prefill(const void* q, const void* k_pages, const voi
                                    const int* tile_seq, const int* tile_row0, int n_tiles, const int* cu_q,
                                    const int* kv_len, const int* block_table, int bt_stride, int n_q_heads,
                                    int n_kv_heads, int head_dim, int page_size, int window, float scale,
-                                   float score_cap, cudaStream_t stream) {
+                                   float score_cap, int chunk, int sink, cudaStream_t stream) {
     if (n_tiles <= 0) return NI_OK;
-    if (n_q_heads <= 0 || n_kv_heads <= 0 || n_q_heads % n_kv_heads || page_size <= 0)
+    if (n_q_heads <= 0 || n_kv_heads <= 0 || n_q_heads % n_kv_heads || page_size <= 0 || chunk < 0)
         return NI_ERR_BAD_ARGUMENT;
     const bool cap = score_cap > 0.f;
     const float sl = cap ? 2.f * 1.4426950408889634f * scale / score_cap : scale * 1.4426950408889634f;
     const float cl = cap ? score_cap * 1.4426950408889634f : 0.f;
 #define GO(HD)                                                                                                         \
     return cap ? launch_prefill<HD, true>(q, k_pages, v_pages, out, tile_seq, tile_row0, n_tiles, cu_q, kv_len,       \
-                                          block_table, bt_stride, n_q_heads, n_kv_heads, page_size, window, sl, cl, stream) \
+                                          block_table, bt_stride, n_q_heads, n_kv_heads, page_size, window, sl, cl, chunk, sink, stream) \
                : launch_prefill<HD, false>(q, k_pages, v_pages, out, tile_seq, tile_row0, n_tiles, cu_q, kv_len,      \
-                                           block_table, bt_stride, n_q_heads, n_kv_heads, page_size, window, sl, cl, stream)
+                                           block_table, bt_stride, n_q_heads, n_kv_heads, page_size, window, sl, cl, chunk, sink, stream)
     switch (head_dim) {
         case 16: GO(16);
         case 32: GO(32);

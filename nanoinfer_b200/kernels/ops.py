@@ -103,6 +103,7 @@ _SIGNATURES = {
     "attention_decode": {
         "ni_attention_decode": [_P, _P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _I, _P, _P, _P, _LL, _P, _LL, _P],
         "ni_attention_decode_capped": [_P, _P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _F, _I, _P, _P, _P, _LL, _P, _LL, _P],
+        "ni_attention_decode_masked": [_P, _P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _F, _I, _I, _I, _P, _P, _P, _LL, _P, _LL, _P],
         "ni_attention_decode_balanced": [_P, _P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _P, _P, _P, _LL, _P, _LL, _P],
         "ni_attention_decode_fresh_keys": [],
         "ni_attention_decode_set_cluster_merge": [_I],
@@ -110,7 +111,7 @@ _SIGNATURES = {
         "ni_attention_decode_noalloc": [_P, _P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _I, _P],
     },
     "attention_prefill": {
-        "ni_attention_prefill": [_P, _P, _P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _F, _P],
+        "ni_attention_prefill": [_P, _P, _P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _F, _I, _I, _P],
     },
     "attention_prefill_tc": {
         "ni_attention_prefill_tc": [_P, _P, _P, _P, _I, _I, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _P, _P],
@@ -1339,9 +1340,10 @@ def attention_decode_cluster_merge(on: bool) -> None:
 
 def attention_decode(q, k_pages, v_pages, out, token_list, n_items, positions, seq_of_token, block_table,
                      n_q_heads, n_kv_heads, head_dim, page_size, window, scale, n_splits, scratch,
-                     tickets, warm=(), score_cap: float = 0.0) -> None:
+                     tickets, warm=(), score_cap: float = 0.0, chunk: int = 0, sink: bool = False) -> None:
     """Split-K attention of single query tokens (bfloat16).  ``score_cap`` c > 0 bounds the scaled scores:
-    s <- c * tanh(s / c).  ``token_list`` int32 [n_items] or
+    s <- c * tanh(s / c).  ``chunk`` c > 0: the token at position p sees only the keys from p - p % c on; ``sink``: one
+    is added to the softmax's denominator.  ``token_list`` int32 [n_items] or
     None for tokens 0..n_items-1.  scratch: float32, at least n_items * Hq * n_splits *
     (head_dim + 2); tickets: int32 zeros, at least n_items * Hkv (left zero by the kernel).
     ``warm``: up to two (tensor, first byte, bytes) (weights that the kernels after it read): the
@@ -1353,6 +1355,17 @@ def attention_decode(q, k_pages, v_pages, out, token_list, n_items, positions, s
         raise KernelError("attention_decode: scratch or tickets too small")
     lib = load("attention_decode")
     capped = score_cap and score_cap > 0.0
+    if chunk or sink:
+        _check(lib.ni_attention_decode_masked(
+            _dev(q, "q", torch.bfloat16), _dev(k_pages, "k_pages", torch.bfloat16),
+            _dev(v_pages, "v_pages", torch.bfloat16), _dev(out, "out", torch.bfloat16),
+            _dev(token_list, "token_list", torch.int32) if token_list is not None else None, n_items,
+            _dev(positions, "positions", torch.int32), _dev(seq_of_token, "seq_of_token", torch.int32),
+            _dev(block_table, "block_table", torch.int32), block_table.shape[1], n_q_heads, n_kv_heads,
+            head_dim, page_size, int(window) if window else 0, float(scale), float(score_cap or 0.0), int(chunk or 0),
+            1 if sink else 0, n_splits, _dev(scratch, "scratch", torch.float32), _dev(tickets, "tickets", torch.int32),
+            *regions, _stream()), "attention_decode")
+        return
     _check((lib.ni_attention_decode_capped if capped else lib.ni_attention_decode)(
         _dev(q, "q", torch.bfloat16), _dev(k_pages, "k_pages", torch.bfloat16),
         _dev(v_pages, "v_pages", torch.bfloat16), _dev(out, "out", torch.bfloat16),
@@ -1374,15 +1387,17 @@ def attention_prefill_tc_supports(n_q_heads: int, n_kv_heads: int, head_dim: int
 
 def attention_prefill(q, k_pages, v_pages, out, tile_seq, tile_row0, n_tiles, cu_q, kv_len, block_table,
                       n_q_heads, n_kv_heads, head_dim, page_size, window, scale, kernel: Optional[str] = None,
-                      score_cap: float = 0.0) -> None:
-    """``score_cap`` c > 0 bounds the scaled scores, s <- c * tanh(s / c) (the mma.sync kernel only).
+                      score_cap: float = 0.0, chunk: int = 0, sink: bool = False) -> None:
+    """``score_cap`` c > 0 bounds the scaled scores, s <- c * tanh(s / c) (the mma.sync kernel only).  ``chunk`` c > 0:
+    a query at position p sees only the keys from p - p % c on; ``sink``: one is added to the softmax's denominator
+    (both: the mma.sync kernel only).
     Flash-style causal attention of prompt portions (bfloat16): one block per tile of
     PREFILL_TILE_ROWS query rows and query head (mma.sync kernel) or pair of query heads
     (tcgen05 kernel, where it takes the case); tile_seq / tile_row0 int32 [n_tiles] name each
     tile's request and first row.  ``kernel``: "tc" or "mma" to insist on one of the two."""
     if head_dim % 16 or head_dim > PREFILL_MAX_HEAD_DIM:
         raise KernelError(f"attention_prefill: head_dim {head_dim} not supported (multiples of 16 up to 128)")
-    tc_ok = attention_prefill_tc_supports(n_q_heads, n_kv_heads, head_dim, page_size) and not score_cap
+    tc_ok = attention_prefill_tc_supports(n_q_heads, n_kv_heads, head_dim, page_size) and not score_cap and not chunk and not sink
     if kernel == "tc" and not tc_ok:
         raise KernelError("attention_prefill: the tcgen05 kernel does not take this case")
     if tc_ok and kernel != "mma":
@@ -1401,8 +1416,8 @@ def attention_prefill(q, k_pages, v_pages, out, tile_seq, tile_row0, n_tiles, cu
         _dev(tile_seq, "tile_seq", torch.int32), _dev(tile_row0, "tile_row0", torch.int32), n_tiles,
         _dev(cu_q, "cu_q", torch.int32), _dev(kv_len, "kv_len", torch.int32),
         _dev(block_table, "block_table", torch.int32), block_table.shape[1], n_q_heads, n_kv_heads,
-        head_dim, page_size, int(window) if window else 0, float(scale), float(score_cap or 0.0), _stream()),
-        "attention_prefill")
+        head_dim, page_size, int(window) if window else 0, float(scale), float(score_cap or 0.0), int(chunk or 0),
+        1 if sink else 0, _stream()), "attention_prefill")
 
 
 _argmax_keys: Dict[torch.device, torch.Tensor] = {}   # per device: merge keys, zero between calls

@@ -54,10 +54,6 @@ class PagedAttendMixin:
                          "tile_row0": np.asarray([t[2] for t in tiles], dtype=i32)},
                         {"n_dec": len(dec), "n_tiles": len(tiles)})
 
-    def _fast_attention(self, chunk: int, sink: bool) -> bool:
-        """True if the tensor-core attention kernels compute this mixer's mask and denominator."""
-        return chunk == 0 and not sink
-
     def _attend(self, q, cache, att, ctx, table) -> None:
         """Attention of every token of the step over its own request's pages.
 
@@ -70,9 +66,10 @@ class PagedAttendMixin:
         slopes = getattr(self.position, "head_slopes", None)
         cap = float(getattr(self, "score_cap", 0.0))       # > 0: scores are bounded by cap * tanh(s / cap)
         chunk, sink = int(getattr(self, "chunk", 0) or 0), bool(getattr(self, "sink", False))
-        if rt.dtype != torch.bfloat16 or slopes is not None or not self._fast_attention(chunk, sink):
-            # float32, or a position encoding that acts on the scores (a bias slope[h] * (k_pos - q_pos)), or a mask
-            # or denominator that the tensor-core kernels do not know: the plain kernel takes them all
+        if rt.dtype != torch.bfloat16 or slopes is not None:
+            # float32, or a position encoding that acts on the scores (a bias slope[h] * (k_pos - q_pos)): the plain
+            # kernel takes both.  (A chunk mask and a sink are known to the split-K kernel for single tokens and to the
+            # flash-style mma.sync kernel for prompt portions, not to the balanced and the tcgen05 kernels.)
             ops.attention_generic(q, cache.k_pages, cache.v_pages, att, ctx.positions, ctx.seq_of_token,
                                   table, *common, head_slopes=slopes, score_cap=cap, chunk=chunk, sink=sink)
             return
@@ -82,7 +79,7 @@ class PagedAttendMixin:
         n_dec = n if plan is None else plan.scalars["n_dec"]
         dec_list = None if plan is None else plan.arrays["dec_tokens"]
         if n_dec > 0:
-            if (decode_ok and cap == 0.0 and rt.balanced_attention(n_dec, self.n_kv, self.head_dim)
+            if (decode_ok and cap == 0.0 and chunk == 0 and not sink and rt.balanced_attention(n_dec, self.n_kv, self.head_dim)
                     and n_dec <= ops.DECODE_BALANCED_MAX_ITEMS):
                 # many tokens: their keys dealt evenly over a fixed set of blocks, whatever their lengths
                 scratch = rt.workspace("attention_decode_balanced_partials",
@@ -98,18 +95,18 @@ class PagedAttendMixin:
                 tickets = rt.workspace("attention_decode_tickets", n_dec * self.n_kv, torch.int32, zero=True)
                 ops.attention_decode(q, cache.k_pages, cache.v_pages, att, dec_list, n_dec, ctx.positions,
                                      ctx.seq_of_token, table, *common, splits, scratch, tickets,
-                                     warm=rt.warm_attention(self.w_o, ctx), score_cap=cap)
+                                     warm=rt.warm_attention(self.w_o, ctx), score_cap=cap, chunk=chunk, sink=sink)
             else:
                 ops.attention_generic(q, cache.k_pages, cache.v_pages, att, ctx.positions, ctx.seq_of_token,
-                                      table, *common, token_list=dec_list, score_cap=cap)
+                                      table, *common, token_list=dec_list, score_cap=cap, chunk=chunk, sink=sink)
         if plan is not None and plan.scalars["n_tiles"] > 0:
             if prefill_ok:
                 ops.attention_prefill(q, cache.k_pages, cache.v_pages, att, plan.arrays["tile_seq"],
                                       plan.arrays["tile_row0"], plan.scalars["n_tiles"], ctx.cu_q, ctx.kv_len, table,
-                                      *common, score_cap=cap)
+                                      *common, score_cap=cap, chunk=chunk, sink=sink)
             else:
                 ops.attention_generic(q, cache.k_pages, cache.v_pages, att, ctx.positions, ctx.seq_of_token,
-                                      table, *common, token_list=plan.arrays["long_tokens"], score_cap=cap)
+                                      table, *common, token_list=plan.arrays["long_tokens"], score_cap=cap, chunk=chunk, sink=sink)
 
 
 class PagedAttention(PagedAttendMixin, Part):

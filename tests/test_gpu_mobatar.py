@@ -299,12 +299,13 @@ def test_window_edges(tmp_path, dtype, window, n, kind):
 
 
 @pytest.mark.parametrize("kind", ["prompt", "decoded"])
-@pytest.mark.parametrize("chunk, n", [(24, 60), (6, 40), (16, 50), (19, 70)])
+@pytest.mark.parametrize("chunk, n, D, V", [(24, 60, 16, 24), (6, 40, 16, 24), (16, 50, 64, 64), (19, 70, 16, 24), (19, 70, 128, 128),
+                                            (70, 150, 64, 64)])
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-def test_chunk_edges(tmp_path, dtype, chunk, n, kind):
+def test_chunk_edges(tmp_path, dtype, chunk, n, D, V, kind):
     """Chunk-masked attention alone (the other side's scale is 0): the first token of the end's chunk counts, the
-    last one of the chunk before cannot."""
-    layer = tm.side_by_side(tm.chunked(4, 2, 16, 24, tm.rot(8, 5000.0, {"factor": 2.0}), 1.2, chunk),
+    last one of the chunk before cannot.  Heads of 64 and 128 take the tensor-core kernels in bfloat16."""
+    layer = tm.side_by_side(tm.chunked(4, 2, D, V, tm.rot(8, 5000.0, {"factor": 2.0}), 1.2 * (16 / D) ** 0.5, chunk),
                             tm.retention(2, 8, 8, (0.9, 0.9), None), 1.0, 0.0, None)
     d = str(tmp_path / "m")
     tm.write_model(d, _one_layer(layer), chunk, tune=_loud(("l0.mix.left.o", 4.0)))
