@@ -221,6 +221,8 @@ struct AtParams {
     int bt_stride, n_q_heads, n_kv_heads, page_size, window;
     float scale_log2e;
     int* error;
+    int chunk;                     // > 0: a query at position p sees only the keys from p - p % chunk on
+    int sink;                      // != 0: one is added to every row's softmax denominator (a key of score 0 without a value)
 };
 
 template <int HD, int STAGES>
@@ -277,7 +279,9 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     const int rows = min(AT_BM, q_len - row0);
     const int first_pos = kv_start + row0, last_pos = first_pos + rows - 1;
     const int j_end = last_pos / AT_BN + 1;
-    const int j_begin = p.window > 0 ? max(0, first_pos - p.window + 1) / AT_BN : 0;
+    int j_first = p.window > 0 ? max(0, first_pos - p.window + 1) / AT_BN : 0;
+    if (p.chunk > 0) j_first = max(j_first, (first_pos - first_pos % p.chunk) / AT_BN);     // the first row's chunk starts first
+    const int j_begin = j_first;
     const int n_tiles = j_end - j_begin;
     const int G = p.n_q_heads / p.n_kv_heads;
     // A kv head's group of query heads is cut into blocks of two (the two streams).  The last
@@ -495,9 +499,11 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             const int kbase = (j_begin + i) * AT_BN + 64 * half;        // key of this thread's column 0
             // visible columns of this row among its 64: [c_lo, c_hi)
             const int c_hi = min(64, pos - kbase + 1);
-            const int c_lo = p.window > 0 ? max(0, pos - p.window + 1 - kbase) : 0;
+            int c_lo = p.window > 0 ? max(0, pos - p.window + 1 - kbase) : 0;
+            if (p.chunk > 0) c_lo = max(c_lo, pos - pos % p.chunk - kbase);
             const int tile_k0 = (j_begin + i) * AT_BN;
-            const bool masked = (tile_k0 + AT_BN - 1 > first_pos) || (p.window > 0 && tile_k0 < last_pos - p.window + 1);
+            const bool masked = (tile_k0 + AT_BN - 1 > first_pos) || (p.window > 0 && tile_k0 < last_pos - p.window + 1) ||
+                                (p.chunk > 0 && tile_k0 < last_pos - last_pos % p.chunk);
             // the row's 64 scores of this half, read once
             uint32_t v[64];
             at_ld32_async(t_s, v);
@@ -596,6 +602,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             at_mbar_arrive(&p_full[s]);
         }
         // ---- the finished rows: O / l -> bfloat16; the row's sum is the two halves' together ----
+        if (p.sink && half == 0) l += at_exp2(-(m_used == -INFINITY ? 0.f : m_used));      // the sink's weight, counted once per row
         row_max[0][s][half][r] = l;                        // (the buffer of an even tile; see below)
         if (ok && n_tiles > 0 &&
             __all_sync(0xffffffffu, at_wait(&o_done[s], (uint32_t)(n_tiles - 1) & 1u, abort_flag, p.error, AT_ERR_SOFTMAX))) {
@@ -709,13 +716,15 @@ NI_EXPORT int ni_attention_prefill_tc_supports(int n_q_heads, int n_kv_heads, in
 // q, out: bf16 [n_tokens, Hq * hd]; k_pages, v_pages: bf16 [n_pages, Hkv, page_size, hd], all 16-byte
 // aligned.  tile_seq / tile_row0 [n_tiles]: request and first query row of each block's 128 rows.
 // error: a device int, zero on entry; non-zero afterwards if a wait inside the kernel ran out.
-NI_EXPORT int ni_attention_prefill_tc(const void* q, const void* k_pages, const void* v_pages, void* out, int n_tokens,
-                                      int n_pages, const int* tile_seq, const int* tile_row0, int n_tiles,
-                                      const int* cu_q, const int* kv_len, const int* block_table, int bt_stride,
-                                      int n_q_heads, int n_kv_heads, int head_dim, int page_size, int window,
-                                      float scale, int* error, cudaStream_t stream) {
+// chunk > 0: a query at position p sees only the keys from p - p % chunk on; sink != 0: one is added to the softmax's
+// denominator.
+NI_EXPORT int ni_attention_prefill_tc_masked(const void* q, const void* k_pages, const void* v_pages, void* out, int n_tokens,
+                                             int n_pages, const int* tile_seq, const int* tile_row0, int n_tiles,
+                                             const int* cu_q, const int* kv_len, const int* block_table, int bt_stride,
+                                             int n_q_heads, int n_kv_heads, int head_dim, int page_size, int window,
+                                             float scale, int chunk, int sink, int* error, cudaStream_t stream) {
     if (n_tiles <= 0) return NI_OK;
-    if (n_tokens <= 0 || n_pages <= 0 || error == nullptr) return NI_ERR_BAD_ARGUMENT;
+    if (n_tokens <= 0 || n_pages <= 0 || error == nullptr || chunk < 0) return NI_ERR_BAD_ARGUMENT;
     if (!ni_attention_prefill_tc_supports(n_q_heads, n_kv_heads, head_dim, page_size)) return NI_ERR_UNSUPPORTED_SIZE;
     if (((uintptr_t)q & 15) || ((uintptr_t)k_pages & 15) || ((uintptr_t)v_pages & 15) || ((uintptr_t)out & 15))
         return NI_ERR_UNSUPPORTED_SIZE;
@@ -731,6 +740,17 @@ NI_EXPORT int ni_attention_prefill_tc(const void* q, const void* k_pages, const 
     p.out = (__nv_bfloat16*)out; p.tile_seq = tile_seq; p.tile_row0 = tile_row0; p.cu_q = cu_q; p.kv_len = kv_len;
     p.block_table = block_table; p.bt_stride = bt_stride; p.n_q_heads = n_q_heads; p.n_kv_heads = n_kv_heads;
     p.page_size = page_size; p.window = window; p.scale_log2e = scale * 1.4426950408889634f; p.error = error;
+    p.chunk = chunk; p.sink = sink;
     if (head_dim == 64) return launch_at<64, 4>(mq, mk, mv, p, n_tiles, stream);
     return launch_at<128, 2>(mq, mk, mv, p, n_tiles, stream);
+}
+
+NI_EXPORT int ni_attention_prefill_tc(const void* q, const void* k_pages, const void* v_pages, void* out, int n_tokens,
+                                      int n_pages, const int* tile_seq, const int* tile_row0, int n_tiles,
+                                      const int* cu_q, const int* kv_len, const int* block_table, int bt_stride,
+                                      int n_q_heads, int n_kv_heads, int head_dim, int page_size, int window,
+                                      float scale, int* error, cudaStream_t stream) {
+    return ni_attention_prefill_tc_masked(q, k_pages, v_pages, out, n_tokens, n_pages, tile_seq, tile_row0, n_tiles, cu_q, kv_len,
+                                          block_table, bt_stride, n_q_heads, n_kv_heads, head_dim, page_size, window, scale, 0, 0,
+                                          error, stream);
 }

@@ -49,8 +49,27 @@ __global__ void cast_bf16_kernel(const float* __restrict__ x, __nv_bfloat16* __r
     if (i < n) out[i] = __float2bfloat16_rn(x[i]);
 }
 
+// The same, eight numbers per thread (n a multiple of 8, both on 16 bytes).
+__global__ void cast_bf16_vec_kernel(const float4* __restrict__ x, uint4* __restrict__ out, long long n8) {
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n8) return;
+    const float4 a = x[2 * i], b = x[2 * i + 1];
+    const __nv_bfloat162 p0 = __floats2bfloat162_rn(a.x, a.y), p1 = __floats2bfloat162_rn(a.z, a.w);
+    const __nv_bfloat162 p2 = __floats2bfloat162_rn(b.x, b.y), p3 = __floats2bfloat162_rn(b.z, b.w);
+    uint4 o;
+    o.x = *reinterpret_cast<const uint32_t*>(&p0); o.y = *reinterpret_cast<const uint32_t*>(&p1);
+    o.z = *reinterpret_cast<const uint32_t*>(&p2); o.w = *reinterpret_cast<const uint32_t*>(&p3);
+    out[i] = o;
+}
+
 NI_EXPORT int ni_cast_bf16(const float* x, void* out, long long n, cudaStream_t stream) {
     if (n <= 0) return NI_OK;
+    if (n % 8 == 0 && ((reinterpret_cast<size_t>(x) | reinterpret_cast<size_t>(out)) & 15) == 0) {
+        const long long n8 = n / 8, vb = (n8 + 255) / 256;
+        if (vb > 2147483647LL) return NI_ERR_UNSUPPORTED_SIZE;
+        cast_bf16_vec_kernel<<<(int)vb, 256, 0, stream>>>((const float4*)x, (uint4*)out, n8);
+        NI_RETURN_LAUNCH_STATUS();
+    }
     const long long blocks = (n + 255) / 256;
     if (blocks > 2147483647LL) return NI_ERR_UNSUPPORTED_SIZE;
     cast_bf16_kernel<<<(int)blocks, 256, 0, stream>>>(x, (__nv_bfloat16*)out, n);
@@ -59,9 +78,11 @@ NI_EXPORT int ni_cast_bf16(const float* x, void* out, long long n, cudaStream_t 
 
 // h[t, :] += z / sqrt(mean(z^2) + eps) * weight with z = y[t, :] (+ bias, FP32 [d], where one is given: a product's
 // bias that its kernel did not add)
+// `rounded` (bfloat16 [rows, d], or null): the updated row once more in bfloat16 - what the next sublayer reads when it
+// takes the stream itself.
 template <typename T>
 __global__ void add_normed_kernel(float* __restrict__ h, const T* __restrict__ y, const float* __restrict__ weight,
-                                  float eps, int d, const float* __restrict__ bias) {
+                                  float eps, int d, const float* __restrict__ bias, __nv_bfloat16* __restrict__ rounded) {
     __shared__ float scratch[32];
     const int t = blockIdx.x;
     const T* yr = y + (size_t)t * d;
@@ -73,14 +94,18 @@ __global__ void add_normed_kernel(float* __restrict__ h, const T* __restrict__ y
     }
     ss = ni_block_sum(ss, scratch);
     const float inv = 1.0f / sqrtf(ss / (float)d + eps);
-    for (int i = threadIdx.x; i < d; i += blockDim.x) hr[i] += (ni_to_float(yr[i]) + (bias ? bias[i] : 0.f)) * inv * weight[i];
+    for (int i = threadIdx.x; i < d; i += blockDim.x) {
+        const float v = hr[i] + (ni_to_float(yr[i]) + (bias ? bias[i] : 0.f)) * inv * weight[i];
+        hr[i] = v;
+        if (rounded) rounded[(size_t)t * d + i] = __float2bfloat16_rn(v);
+    }
 }
 
 // The same for FP32 y whose width is a multiple of 4, up to 4,096: the row stays in the block's registers between
 // the sum of squares and the addition, and moves in 16-byte pieces.
 __global__ void __launch_bounds__(256)
 add_normed_f32_vec_kernel(float* __restrict__ h, const float* __restrict__ y, const float* __restrict__ weight, float eps,
-                          int d, const float* __restrict__ bias) {
+                          int d, const float* __restrict__ bias, __nv_bfloat16* __restrict__ rounded) {
     __shared__ float scratch[32];
     const int t = blockIdx.x;
     const float4* yr = reinterpret_cast<const float4*>(y + (size_t)t * d);
@@ -112,21 +137,30 @@ add_normed_f32_vec_kernel(float* __restrict__ h, const float* __restrict__ y, co
             a.z += v[r].z * inv * g.z;
             a.w += v[r].w * inv * g.w;
             hr[i] = a;
+            if (rounded) {
+                const __nv_bfloat162 lo = __floats2bfloat162_rn(a.x, a.y), hi = __floats2bfloat162_rn(a.z, a.w);
+                uint2 packed;
+                packed.x = *reinterpret_cast<const uint32_t*>(&lo);
+                packed.y = *reinterpret_cast<const uint32_t*>(&hi);
+                reinterpret_cast<uint2*>(rounded + (size_t)t * d)[i] = packed;
+            }
         }
     }
 }
 
 NI_EXPORT int ni_add_normed(float* h, const void* y, int y_dtype, const float* weight, float eps, int n_rows, int d,
-                            const float* bias, cudaStream_t stream) {
+                            const float* bias, void* rounded, cudaStream_t stream) {
     if (n_rows <= 0) return NI_OK;
     if (d <= 0) return NI_ERR_BAD_ARGUMENT;
     const int threads = d >= 1024 ? 256 : 128;
-    if (y_dtype == NI_DTYPE_F32 && d % 4 == 0 && d <= 4096 && d >= 512 && (reinterpret_cast<size_t>(bias) & 15) == 0)
-        add_normed_f32_vec_kernel<<<n_rows, 256, 0, stream>>>(h, (const float*)y, weight, eps, d, bias);
+    __nv_bfloat16* rb = (__nv_bfloat16*)rounded;
+    if (y_dtype == NI_DTYPE_F32 && d % 4 == 0 && d <= 4096 && d >= 512 && (reinterpret_cast<size_t>(bias) & 15) == 0 &&
+        (reinterpret_cast<size_t>(rounded) & 7) == 0)
+        add_normed_f32_vec_kernel<<<n_rows, 256, 0, stream>>>(h, (const float*)y, weight, eps, d, bias, rb);
     else if (y_dtype == NI_DTYPE_F32)
-        add_normed_kernel<float><<<n_rows, threads, 0, stream>>>(h, (const float*)y, weight, eps, d, bias);
+        add_normed_kernel<float><<<n_rows, threads, 0, stream>>>(h, (const float*)y, weight, eps, d, bias, rb);
     else if (y_dtype == NI_DTYPE_BF16)
-        add_normed_kernel<__nv_bfloat16><<<n_rows, threads, 0, stream>>>(h, (const __nv_bfloat16*)y, weight, eps, d, bias);
+        add_normed_kernel<__nv_bfloat16><<<n_rows, threads, 0, stream>>>(h, (const __nv_bfloat16*)y, weight, eps, d, bias, rb);
     else
         return NI_ERR_BAD_ARGUMENT;
     NI_RETURN_LAUNCH_STATUS();

@@ -115,6 +115,11 @@ class DecoderModel:
                     ops.add_row(h, self.stream_inputs[run.stream_input])
             ctx.read_after, ctx.norm_after = self._read_after[r], self._norm_after[r]
             delta = self.blocks[run.layer].forward(h, delta, ctx, caches[r])
+            if isinstance(delta, ops.StreamCopy):
+                # the stream is up to date; its bfloat16 copy goes on only to a block that reads the stream itself
+                nxt = cfg.schedule[r + 1] if r + 1 < len(cfg.schedule) else None
+                if nxt is None or nxt.stream_input is not None or not getattr(self.blocks[nxt.layer], "takes_stream_copy", False):
+                    delta = None
         ctx.read_after, ctx.norm_after = (), None
         if h is None:
             h = h0

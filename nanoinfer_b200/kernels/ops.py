@@ -43,7 +43,7 @@ _SIGNATURES = {
     "pointwise": {
         "ni_embedding_sinusoid": [_P, _P, _P, _I, _P, _P, _I, _I, _I, _P],
         "ni_cast_bf16": [_P, _P, _LL, _P],
-        "ni_add_normed": [_P, _P, _I, _P, _F, _I, _I, _P, _P],
+        "ni_add_normed": [_P, _P, _I, _P, _F, _I, _I, _P, _P, _P],
         "ni_polynorm": [_P, _I, _P, _F, _P, _I, _I, _P],
         "ni_gelu_table_gate": [_P, _I, _P, _P, _I, _P, _I, _I, _I, _I, _I, _P],
         "ni_add_row": [_P, _P, _I, _I, _I, _P],
@@ -115,6 +115,7 @@ _SIGNATURES = {
     },
     "attention_prefill_tc": {
         "ni_attention_prefill_tc": [_P, _P, _P, _P, _I, _I, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _P, _P],
+        "ni_attention_prefill_tc_masked": [_P, _P, _P, _P, _I, _I, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _I, _I, _P, _P],
         "ni_attention_prefill_tc_supports": [_I, _I, _I, _I],
         "ni_attention_prefill_tc_set_wait": [_LL, _I],
     },
@@ -422,15 +423,19 @@ def cast_bf16(x: torch.Tensor, out: torch.Tensor) -> None:
                                           _stream()), "cast_bf16")
 
 
-def add_normed(h: torch.Tensor, y: torch.Tensor, weight: torch.Tensor, eps: float, bias: Optional[torch.Tensor] = None) -> None:
+def add_normed(h: torch.Tensor, y: torch.Tensor, weight: torch.Tensor, eps: float, bias: Optional[torch.Tensor] = None,
+               rounded: Optional[torch.Tensor] = None) -> None:
     """h += z / sqrt(mean(z^2) + eps) * weight, row by row, with z = y (+ ``bias`` float32 [d], if given); h float32
-    [T, d], weight float32 [d]."""
+    [T, d], weight float32 [d].  ``rounded`` (bfloat16 [T, d]): also receives the updated h, rounded."""
     n, d = h.shape
-    if y.shape != h.shape or weight.numel() != d or (bias is not None and bias.numel() != d):
+    if y.shape != h.shape or weight.numel() != d or (bias is not None and bias.numel() != d) or \
+            (rounded is not None and rounded.shape != h.shape):
         raise KernelError("add_normed: shapes do not agree")
     _check(load("pointwise").ni_add_normed(_dev(h, "h", torch.float32), _dev(y, "y"), _code(y, "y"),
                                            _dev(weight, "weight", torch.float32), float(eps), n, d,
-                                           _dev(bias, "bias", torch.float32) if bias is not None else None, _stream()), "add_normed")
+                                           _dev(bias, "bias", torch.float32) if bias is not None else None,
+                                           _dev(rounded, "rounded", torch.bfloat16) if rounded is not None else None,
+                                           _stream()), "add_normed")
 
 
 def polynorm(z: torch.Tensor, coef: torch.Tensor, eps: float, out: torch.Tensor) -> None:
@@ -945,6 +950,15 @@ class NormHandoff:
         return self.ssq.data_ptr(), self.parts, self.eps
 
 
+class StreamCopy:
+    """What a block may hand to the block after it instead of a pending addition: the stream is up to date, and
+    ``rounded`` is its bfloat16 copy, written by the kernel that last added into the stream.  The model passes it on
+    only to a block that says ``takes_stream_copy``."""
+
+    def __init__(self, stream: torch.Tensor, rounded: torch.Tensor) -> None:
+        self.stream, self.rounded = stream, rounded
+
+
 _NO_HANDOFF = (None, None, None, 0)
 _NO_PRE = (None, 0, 0.0)
 
@@ -1390,25 +1404,25 @@ def attention_prefill(q, k_pages, v_pages, out, tile_seq, tile_row0, n_tiles, cu
                       score_cap: float = 0.0, chunk: int = 0, sink: bool = False) -> None:
     """``score_cap`` c > 0 bounds the scaled scores, s <- c * tanh(s / c) (the mma.sync kernel only).  ``chunk`` c > 0:
     a query at position p sees only the keys from p - p % c on; ``sink``: one is added to the softmax's denominator
-    (both: the mma.sync kernel only).
+    (both kernels).
     Flash-style causal attention of prompt portions (bfloat16): one block per tile of
     PREFILL_TILE_ROWS query rows and query head (mma.sync kernel) or pair of query heads
     (tcgen05 kernel, where it takes the case); tile_seq / tile_row0 int32 [n_tiles] name each
     tile's request and first row.  ``kernel``: "tc" or "mma" to insist on one of the two."""
     if head_dim % 16 or head_dim > PREFILL_MAX_HEAD_DIM:
         raise KernelError(f"attention_prefill: head_dim {head_dim} not supported (multiples of 16 up to 128)")
-    tc_ok = attention_prefill_tc_supports(n_q_heads, n_kv_heads, head_dim, page_size) and not score_cap and not chunk and not sink
+    tc_ok = attention_prefill_tc_supports(n_q_heads, n_kv_heads, head_dim, page_size) and not score_cap
     if kernel == "tc" and not tc_ok:
         raise KernelError("attention_prefill: the tcgen05 kernel does not take this case")
     if tc_ok and kernel != "mma":
-        _check(load("attention_prefill_tc").ni_attention_prefill_tc(
+        _check(load("attention_prefill_tc").ni_attention_prefill_tc_masked(
             _dev(q, "q", torch.bfloat16), _dev(k_pages, "k_pages", torch.bfloat16),
             _dev(v_pages, "v_pages", torch.bfloat16), _dev(out, "out", torch.bfloat16), q.shape[0], k_pages.shape[0],
             _dev(tile_seq, "tile_seq", torch.int32), _dev(tile_row0, "tile_row0", torch.int32), n_tiles,
             _dev(cu_q, "cu_q", torch.int32), _dev(kv_len, "kv_len", torch.int32),
             _dev(block_table, "block_table", torch.int32), block_table.shape[1], n_q_heads, n_kv_heads,
-            head_dim, page_size, int(window) if window else 0, float(scale), _error_word(q.device).data_ptr(),
-            _stream()), "attention_prefill_tc")
+            head_dim, page_size, int(window) if window else 0, float(scale), int(chunk or 0), 1 if sink else 0,
+            _error_word(q.device).data_ptr(), _stream()), "attention_prefill_tc")
         return
     _check(load("attention_prefill").ni_attention_prefill(
         _dev(q, "q", torch.bfloat16), _dev(k_pages, "k_pages", torch.bfloat16),

@@ -7,7 +7,7 @@ import torch
 
 from ..config.registry import part, register_part
 from ..kernels import ops
-from ..kernels.ops import NormHandoff
+from ..kernels.ops import NormHandoff, StreamCopy
 from .base import WeightSlot
 
 
@@ -280,6 +280,7 @@ class OutputNormBlock:
     to the kernel that norms and adds the output."""
 
     kernel_modules = ("pointwise",)       # libraries of csrc that this part's kernels live in
+    takes_stream_copy = True              # forward() accepts an ops.StreamCopy in the place of a pending addition
 
     def __init__(self, layer_spec, hidden_size: int, weights_of, rt) -> None:
         self.rt, self.hidden_size = rt, hidden_size
@@ -304,9 +305,13 @@ class OutputNormBlock:
     def first_norm(self):
         return None
 
-    def _input(self, h: torch.Tensor) -> torch.Tensor:
+    def _input(self, h: torch.Tensor, delta) -> torch.Tensor:
+        """What the first sublayer reads: the stream itself (FP32), the bfloat16 copy that the block before left
+        beside it (``StreamCopy``), or a copy made here."""
         if self.rt.dtype == torch.float32:
             return h
+        if isinstance(delta, StreamCopy) and delta.stream is h:
+            return delta.rounded
         x = self.rt.empty(h.shape[0], self.hidden_size)
         ops.cast_bf16(h, x)
         return x
@@ -314,24 +319,29 @@ class OutputNormBlock:
     def forward(self, h: torch.Tensor, delta, ctx, cache):
         if isinstance(delta, NormHandoff):
             delta = None                                   # the stream is up to date; nothing here reads a prepared norm
-        if delta is not None:
+        if delta is not None and not isinstance(delta, StreamCopy):
             ops.residual_add(h, delta)
+            delta = None
         after = ctx.read_after                       # what runs after this block
         ffn = self.feed_forward
+        bf16 = self.rt.dtype == torch.bfloat16
         ctx.read_after = (tuple(getattr(ffn, "weights_in_order", tuple)()) if ffn is not None else ()) + tuple(after)
         try:
-            y = self.mixer.forward(self._input(h), ctx, cache)
+            y = self.mixer.forward(self._input(h, delta), ctx, cache)
         finally:
             ctx.read_after = after
-        ops.add_normed(h, y, self.mixer_norm.gain, self.mixer_norm.eps)
+        # the kernel that norms and adds a sublayer's output also leaves the new stream in bfloat16: the next reader's input
+        x = self.rt.empty(h.shape[0], self.hidden_size) if bf16 else None
+        ops.add_normed(h, y, self.mixer_norm.gain, self.mixer_norm.eps, rounded=x)
         if ffn is not None:
             bias = getattr(ffn, "output_bias", None)
             if bias is not None:
-                y = ffn.forward(self._input(h), ctx, bias_taken=True)
+                y = ffn.forward(x if bf16 else h, ctx, bias_taken=True)
             else:
-                y = ffn.forward(self._input(h), ctx)
-            ops.add_normed(h, y, self.ffn_norm.gain, self.ffn_norm.eps, bias=bias)
-        return None
+                y = ffn.forward(x if bf16 else h, ctx)
+            x = self.rt.empty(h.shape[0], self.hidden_size) if bf16 else None
+            ops.add_normed(h, y, self.ffn_norm.gain, self.ffn_norm.eps, bias=bias, rounded=x)
+        return StreamCopy(h, x) if bf16 else None
 
 
 register_part("arrangement", "pre_norm", PreNormBlock, replace=True)

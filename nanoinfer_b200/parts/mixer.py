@@ -68,8 +68,8 @@ class PagedAttendMixin:
         chunk, sink = int(getattr(self, "chunk", 0) or 0), bool(getattr(self, "sink", False))
         if rt.dtype != torch.bfloat16 or slopes is not None:
             # float32, or a position encoding that acts on the scores (a bias slope[h] * (k_pos - q_pos)): the plain
-            # kernel takes both.  (A chunk mask and a sink are known to the split-K kernel for single tokens and to the
-            # flash-style mma.sync kernel for prompt portions, not to the balanced and the tcgen05 kernels.)
+            # kernel takes both.  (A chunk mask and a sink are known to the split-K kernel for single tokens and to both
+            # prompt kernels, not to the balanced single-token kernel.)
             ops.attention_generic(q, cache.k_pages, cache.v_pages, att, ctx.positions, ctx.seq_of_token,
                                   table, *common, head_slopes=slopes, score_cap=cap, chunk=chunk, sink=sink)
             return
