@@ -108,8 +108,8 @@ __device__ __forceinline__ void dec_warm(const unsigned char* p, unsigned long l
 // every split writes its partial result into the shared memory of the cluster's first block, one
 // cluster barrier, and that block merges them in split order - no scratch in global memory, no
 // fence, no ticket.
-// chunk > 0: the token at position p sees only the keys from p - p % chunk on; sink: one is added to the softmax's
-// denominator.
+// chunk > 0: the token at position p sees only the keys from p - p % chunk on; flags bit 0 (sink): one is added to the
+// softmax's denominator; flags bit 1: all kv heads of the launch read the pages' one head.
 // CAP: the scaled scores are bounded smoothly, s <- cap * tanh(s / cap), before the softmax.  The kernel is then
 // handed scale_log2e = 2 log2(e) scale / cap and cap_l2 = cap log2(e): with x = exp2(raw * scale_log2e),
 // cap_l2 - 2 cap_l2 / (x + 1) is the capped score in the exponent's base.
@@ -122,7 +122,11 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
                         int bt_stride, int n_q_heads, int n_kv_heads, int page_size, int window,
                         float scale_log2e, float cap_l2, int n_splits, float* __restrict__ scratch,
                         int* __restrict__ tickets, const unsigned char* __restrict__ warm_a, unsigned long long warm_a_bytes,
-                        const unsigned char* __restrict__ warm_b, unsigned long long warm_b_bytes, int chunk, int sink) {
+                        const unsigned char* __restrict__ warm_b, unsigned long long warm_b_bytes, int chunk, int flags) {
+    // flags: bit 0 - the sink; bit 1 - the pages hold ONE head that all the launch's kv heads share (a compressed cache
+    // whose many query heads are dealt over several "kv heads" of at most 16 rows each)
+    const int sink = flags & 1;
+    const bool shared_pages = (flags & 2) != 0;
     // Weights that the kernels after this one will read (the caller's hint, up to two regions): asked
     // into L2 now, in pieces dealt over the blocks, while this kernel - which waits on latencies
     // more than on bandwidth - leaves the memory system room.  Nothing here depends on the kernel before.
@@ -203,7 +207,8 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
             key = key < k_end ? key : k_end - 1;
             const int pi = page_shift >= 0 ? key >> page_shift : key / page_size;
             const int slot = page_shift >= 0 ? key & (page_size - 1) : key - pi * page_size;
-            const size_t off = (((size_t)page[it] * n_kv_heads + kvh) * page_size + slot) * HD + c * 8;
+            const size_t off = shared_pages ? ((size_t)page[it] * page_size + slot) * HD + c * 8
+                                            : (((size_t)page[it] * n_kv_heads + kvh) * page_size + slot) * HD + c * 8;
             dec_cp_async16(sK + dec_sw<HD>(r, c), k_pages + off);
             dec_cp_async16(sV + dec_sw<HD>(r, c), v_pages + off);
         }
@@ -831,7 +836,7 @@ static int launch_decode_cl(const void* q, const void* k_pages, const void* v_pa
                          int bt_stride, int n_q_heads, int n_kv_heads, int page_size, int window,
                          float scale_log2e, float cap_l2, int n_splits, float* scratch, int* tickets, const void* warm_a,
                          unsigned long long warm_a_bytes, const void* warm_b, unsigned long long warm_b_bytes,
-                         int chunk, int sink, cudaStream_t stream) {
+                         int chunk, int flags, cudaStream_t stream) {
     const size_t kv_smem = (size_t)(16 + 4 * SEG) * HD * sizeof(__nv_bfloat16);
     const size_t smem = kv_smem + (CL ? (size_t)n_splits * (n_q_heads / n_kv_heads) * (HD + 2) * sizeof(float) : 0);
     static size_t configured = 0;
@@ -868,7 +873,7 @@ static int launch_decode_cl(const void* q, const void* k_pages, const void* v_pa
                                        (__nv_bfloat16*)out, token_list, positions, seq_of_token, block_table,
                                        bt_stride, n_q_heads, n_kv_heads, page_size, window, scale_log2e, cap_l2, n_splits,
                                        scratch, tickets, (const unsigned char*)warm_a, warm_a_bytes,
-                                       (const unsigned char*)warm_b, warm_b_bytes, chunk, sink);
+                                       (const unsigned char*)warm_b, warm_b_bytes, chunk, flags);
     return e == cudaSuccess ? NI_OK : (int)e;
 }
 
@@ -886,14 +891,14 @@ static int launch_decode(const void* q, const void* k_pages, const void* v_pages
                          int bt_stride, int n_q_heads, int n_kv_heads, int page_size, int window,
                          float scale_log2e, float cap_l2, int n_splits, float* scratch, int* tickets, const void* warm_a,
                          unsigned long long warm_a_bytes, const void* warm_b, unsigned long long warm_b_bytes,
-                         int chunk, int sink, cudaStream_t stream) {
+                         int chunk, int flags, cudaStream_t stream) {
     const size_t slot_bytes = (size_t)n_splits * (n_q_heads / n_kv_heads) * (HD + 2) * sizeof(float);
     const bool few_blocks = (long long)n_items * n_kv_heads * n_splits <= 2LL * ni_sm_count() && slot_bytes <= 65536;
     if (dec_cluster_merge && n_splits >= 2 && ((n_splits <= 8 && slot_bytes <= DEC_CLUSTER_SLOT_BYTES) || (n_splits <= 16 && few_blocks)))
 #define NI_DEC_GO(CL, CAP)                                                                                          \
     launch_decode_cl<HD, SEG, CL, CAP>(q, k_pages, v_pages, out, token_list, n_items, positions, seq_of_token,          \
                                        block_table, bt_stride, n_q_heads, n_kv_heads, page_size, window, scale_log2e,   \
-                                       cap_l2, n_splits, scratch, tickets, warm_a, warm_a_bytes, warm_b, warm_b_bytes, chunk, sink, stream)
+                                       cap_l2, n_splits, scratch, tickets, warm_a, warm_a_bytes, warm_b, warm_b_bytes, chunk, flags, stream)
         return cap_l2 > 0.f ? NI_DEC_GO(true, true) : NI_DEC_GO(true, false);
     return cap_l2 > 0.f ? NI_DEC_GO(false, true) : NI_DEC_GO(false, false);
 #undef NI_DEC_GO
@@ -909,7 +914,7 @@ static int decode_dispatch(const void* q, const void* k_pages, const void* v_pag
                                   int n_q_heads, int n_kv_heads, int head_dim, int page_size, int window,
                                   float scale, float score_cap, int n_splits, float* scratch, int* tickets,
                                   const void* warm_a, long long warm_a_bytes, const void* warm_b,
-                                  long long warm_b_bytes, int chunk, int sink, cudaStream_t stream) {
+                                  long long warm_b_bytes, int chunk, int flags, cudaStream_t stream) {
     if (n_items <= 0) return NI_OK;
     if (chunk < 0) return NI_ERR_BAD_ARGUMENT;
     if (warm_a_bytes < 0 || (warm_a_bytes & 15) || (warm_a_bytes && (!warm_a || ((uintptr_t)warm_a & 15)))) return NI_ERR_BAD_ARGUMENT;
@@ -930,16 +935,16 @@ static int decode_dispatch(const void* q, const void* k_pages, const void* v_pag
                 return launch_decode<64, 128>(q, k_pages, v_pages, out, token_list, n_items, positions, seq_of_token,
                                               block_table, bt_stride, n_q_heads, n_kv_heads, page_size, window,
                                               scale_log2e, cap_l2, n_splits, scratch, tickets, warm_a, (unsigned long long)warm_a_bytes, warm_b,
-                                              (unsigned long long)warm_b_bytes, chunk, sink, stream);
+                                              (unsigned long long)warm_b_bytes, chunk, flags, stream);
             return launch_decode<64, 64>(q, k_pages, v_pages, out, token_list, n_items, positions, seq_of_token,
                                           block_table, bt_stride, n_q_heads, n_kv_heads, page_size, window,
                                           scale_log2e, cap_l2, n_splits, scratch, tickets, warm_a, (unsigned long long)warm_a_bytes, warm_b,
-                                              (unsigned long long)warm_b_bytes, chunk, sink, stream);
+                                              (unsigned long long)warm_b_bytes, chunk, flags, stream);
         case 128:
             return launch_decode<128, 64>(q, k_pages, v_pages, out, token_list, n_items, positions, seq_of_token,
                                            block_table, bt_stride, n_q_heads, n_kv_heads, page_size, window,
                                            scale_log2e, cap_l2, n_splits, scratch, tickets, warm_a, (unsigned long long)warm_a_bytes, warm_b,
-                                              (unsigned long long)warm_b_bytes, chunk, sink, stream);
+                                              (unsigned long long)warm_b_bytes, chunk, flags, stream);
         default: return NI_ERR_UNSUPPORTED_SIZE;
     }
 }
@@ -956,19 +961,21 @@ NI_EXPORT int ni_attention_decode(const void* q, const void* k_pages, const void
                            warm_a, warm_a_bytes, warm_b, warm_b_bytes, 0, 0, stream);
 }
 
-// The same with a chunk mask (chunk > 0: the token at position p sees only the keys from p - p % chunk on) and, with
-// sink != 0, one added to the softmax's denominator; score_cap 0: scores are not bounded.
+// The same with a chunk mask (chunk > 0: the token at position p sees only the keys from p - p % chunk on) and flags:
+// bit 0 - one is added to the softmax's denominator (a sink); bit 1 - k_pages / v_pages hold ONE head
+// ([P, 1, page_size, hd]) that all n_kv_heads of the call read, so that more than 16 query heads over one shared head
+// can be dealt over several groups of at most 16.  score_cap 0: scores are not bounded.
 NI_EXPORT int ni_attention_decode_masked(const void* q, const void* k_pages, const void* v_pages, void* out,
                                          const int* token_list, int n_items, const int* positions,
                                          const int* seq_of_token, const int* block_table, int bt_stride,
                                          int n_q_heads, int n_kv_heads, int head_dim, int page_size, int window,
-                                         float scale, float score_cap, int chunk, int sink, int n_splits, float* scratch,
+                                         float scale, float score_cap, int chunk, int flags, int n_splits, float* scratch,
                                          int* tickets, const void* warm_a, long long warm_a_bytes, const void* warm_b,
                                          long long warm_b_bytes, cudaStream_t stream) {
     if (score_cap < 0.f) return NI_ERR_BAD_ARGUMENT;
     return decode_dispatch(q, k_pages, v_pages, out, token_list, n_items, positions, seq_of_token, block_table, bt_stride,
                            n_q_heads, n_kv_heads, head_dim, page_size, window, scale, score_cap, n_splits, scratch, tickets,
-                           warm_a, warm_a_bytes, warm_b, warm_b_bytes, chunk, sink != 0, stream);
+                           warm_a, warm_a_bytes, warm_b, warm_b_bytes, chunk, flags & 3, stream);
 }
 
 // The same with the scaled scores bounded by score_cap * tanh(s / score_cap) (score_cap > 0).

@@ -686,11 +686,15 @@ lightning_chunk_out_tc_kernel(const __nv_bfloat16* __restrict__ proj, int ld, co
 
 // A step of single tokens: S <- decay S + k v^T, o = S^T q; every state is read and written once.
 // grid (column tiles of 128, H, requests); a warp owns every 8th row, a lane 4 neighbouring columns.
-template <typename T>
+// ROT (retention): nothing is activated; instead the first rotary_dim dimensions of q and k are rotated by the token's
+// position (dimension i paired with i + rotary_dim / 2, angle float(position) * inv_freq[i]) and k is multiplied by
+// k_scale, all in FP32 from the projection's entries - the single-token form of linear_attention_prepare_kernel.
+template <typename T, bool ROT>
 __global__ void __launch_bounds__(LT_THREADS)
 lightning_token_kernel(const T* __restrict__ proj, int ld, float* __restrict__ state, long long state_stride,
                        const int* __restrict__ cu_q, const int* __restrict__ slots, const float* __restrict__ decay,
-                       float* __restrict__ out, int H, int D, int V) {
+                       float* __restrict__ out, int H, int D, int V, const int* __restrict__ positions,
+                       const float* __restrict__ inv_freq, int rotary_dim, float k_scale) {
     extern __shared__ __align__(16) float sm[];
     float* qs = sm;                          // [D]
     float* ks = qs + D;                      // [D]
@@ -700,14 +704,38 @@ lightning_token_kernel(const T* __restrict__ proj, int ld, float* __restrict__ s
     const int t = cu_q[seq];
     if (cu_q[seq + 1] <= t) return;
     const T* row = proj + (size_t)t * ld;
-    for (int d = tid; d < D; d += LT_THREADS) {
-        qs[d] = lt_act<T>(row[(size_t)head * D + d]);
-        ks[d] = lt_act<T>(row[(size_t)(H + head) * D + d]);
+    if (ROT) {
+        const float pos = (float)positions[t];
+        const int half = rotary_dim >> 1;
+        const T* qrow = row + (size_t)head * D;
+        const T* krow = row + (size_t)(H + head) * D;
+        for (int d = tid; d < D; d += LT_THREADS) {
+            float qv = ni_to_float(qrow[d]), kv = ni_to_float(krow[d]);
+            if (d < rotary_dim) {
+                const bool first = d < half;
+                const int other = first ? d + half : d - half;
+                float sn, cs;
+                sincosf(pos * inv_freq[first ? d : d - half], &sn, &cs);
+                const float qo = ni_to_float(qrow[other]), ko = ni_to_float(krow[other]);
+                qv = first ? qv * cs - qo * sn : qv * cs + qo * sn;
+                kv = first ? kv * cs - ko * sn : kv * cs + ko * sn;
+            }
+            qs[d] = qv;
+            ks[d] = kv * k_scale;
+        }
+    } else {
+        for (int d = tid; d < D; d += LT_THREADS) {
+            qs[d] = lt_act<T>(row[(size_t)head * D + d]);
+            ks[d] = lt_act<T>(row[(size_t)(H + head) * D + d]);
+        }
     }
     const int vc = v0 + lane * 4;
     float vv[4], acc[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-    for (int b = 0; b < 4; ++b) vv[b] = vc + b < V ? lt_act<T>(row[(size_t)2 * H * D + (size_t)head * V + vc + b]) : 0.f;
+    for (int b = 0; b < 4; ++b) {
+        const T raw = vc + b < V ? row[(size_t)2 * H * D + (size_t)head * V + vc + b] : row[0];
+        vv[b] = vc + b < V ? (ROT ? ni_to_float(raw) : lt_act<T>(raw)) : 0.f;
+    }
     __syncthreads();
     const float dec = decay[head];
     float* S = state + (size_t)slots[seq] * state_stride + (size_t)head * D * V;
@@ -858,14 +886,14 @@ NI_EXPORT int ni_lightning_recurrence(const void* proj, int dtype, int ld, float
         const size_t smem = ((size_t)2 * D + (LT_THREADS / 32) * 128) * sizeof(float);
         if (smem > 48 * 1024) return NI_ERR_UNSUPPORTED_SIZE;
         if (activation == 0)
-            lightning_token_kernel<LtPlain><<<grid, LT_THREADS, smem, stream>>>((const LtPlain*)proj, ld, state, state_stride,
-                                                                                 cu_q, slots, decay, out, H, D, V);
+            lightning_token_kernel<LtPlain, false><<<grid, LT_THREADS, smem, stream>>>((const LtPlain*)proj, ld, state, state_stride,
+                                                                                        cu_q, slots, decay, out, H, D, V, nullptr, nullptr, 0, 1.f);
         else if (dtype == NI_DTYPE_F32)
-            lightning_token_kernel<float><<<grid, LT_THREADS, smem, stream>>>((const float*)proj, ld, state, state_stride, cu_q,
-                                                                               slots, decay, out, H, D, V);
+            lightning_token_kernel<float, false><<<grid, LT_THREADS, smem, stream>>>((const float*)proj, ld, state, state_stride, cu_q,
+                                                                                      slots, decay, out, H, D, V, nullptr, nullptr, 0, 1.f);
         else
-            lightning_token_kernel<__nv_bfloat16><<<grid, LT_THREADS, smem, stream>>>((const __nv_bfloat16*)proj, ld, state,
-                                                                                       state_stride, cu_q, slots, decay, out, H, D, V);
+            lightning_token_kernel<__nv_bfloat16, false><<<grid, LT_THREADS, smem, stream>>>(
+                (const __nv_bfloat16*)proj, ld, state, state_stride, cu_q, slots, decay, out, H, D, V, nullptr, nullptr, 0, 1.f);
         NI_RETURN_LAUNCH_STATUS();
     }
     if (buf == nullptr || buf_chunks < ni_lightning_max_chunks(n_tokens, n_seqs)) return NI_ERR_BAD_ARGUMENT;
@@ -1004,6 +1032,33 @@ NI_EXPORT int ni_linear_attention_prepare(const void* proj, int dtype, int ld, c
     else if (dtype == NI_DTYPE_BF16)
         linear_attention_prepare_kernel<__nv_bfloat16><<<n_tokens, threads, smem, stream>>>(
             (const __nv_bfloat16*)proj, ld, positions, inv_freq, k_scale, qkv, H, D, V, rotary_dim);
+    else
+        return NI_ERR_BAD_ARGUMENT;
+    NI_RETURN_LAUNCH_STATUS();
+}
+
+// A step of single tokens of a retention layer in ONE launch: rotation, key scale, state update and read-out, straight
+// from the projection (columns q (H D) | k (H D) | v (H V) | ...); every request brings one token.
+NI_EXPORT int ni_retention_token_step(const void* proj, int dtype, int ld, float* state, long long state_stride,
+                                      const int* cu_q, const int* slots, const float* decay, float* out, int n_seqs, int H,
+                                      int D, int V, const int* positions, const float* inv_freq, int rotary_dim,
+                                      float k_scale, cudaStream_t stream) {
+    if (n_seqs <= 0) return NI_OK;
+    if (H <= 0 || D <= 0 || V <= 0 || ld < 2 * H * D + H * V || state_stride < (long long)H * D * V || rotary_dim < 0 ||
+        rotary_dim > D || (rotary_dim & 1))
+        return NI_ERR_BAD_ARGUMENT;
+    if (H > 65535 || n_seqs > 65535) return NI_ERR_UNSUPPORTED_SIZE;
+    dim3 grid((V + 127) / 128, H, n_seqs);
+    const size_t smem = ((size_t)2 * D + (LT_THREADS / 32) * 128) * sizeof(float);
+    if (smem > 48 * 1024) return NI_ERR_UNSUPPORTED_SIZE;
+    if (dtype == NI_DTYPE_F32)
+        lightning_token_kernel<float, true><<<grid, LT_THREADS, smem, stream>>>((const float*)proj, ld, state, state_stride, cu_q,
+                                                                                 slots, decay, out, H, D, V, positions, inv_freq,
+                                                                                 rotary_dim, k_scale);
+    else if (dtype == NI_DTYPE_BF16)
+        lightning_token_kernel<__nv_bfloat16, true><<<grid, LT_THREADS, smem, stream>>>(
+            (const __nv_bfloat16*)proj, ld, state, state_stride, cu_q, slots, decay, out, H, D, V, positions, inv_freq, rotary_dim,
+            k_scale);
     else
         return NI_ERR_BAD_ARGUMENT;
     NI_RETURN_LAUNCH_STATUS();

@@ -362,10 +362,26 @@ __global__ void capped_glu_vec_kernel(const T* __restrict__ gate_up, T* __restri
     NiVec16<T>::load(row + c, g);
     NiVec16<T>::load(row + inter + c, u);
     const float rs = row_scale ? row_scale[t] : 1.0f;
+    float bg[V], bu[V];
+#pragma unroll
+    for (int k = 0; k < V; ++k) bg[k] = bu[k] = 0.f;
+    if (bias) {                       // 16-byte loads where the two halves of the bias start on 16 bytes
+        if ((inter & 3) == 0 && (reinterpret_cast<size_t>(bias) & 15) == 0) {
+#pragma unroll
+            for (int k = 0; k < V; k += 4) {
+                const float4 a = *reinterpret_cast<const float4*>(bias + c + k), b = *reinterpret_cast<const float4*>(bias + inter + c + k);
+                bg[k] = a.x; bg[k + 1] = a.y; bg[k + 2] = a.z; bg[k + 3] = a.w;
+                bu[k] = b.x; bu[k + 1] = b.y; bu[k + 2] = b.z; bu[k + 3] = b.w;
+            }
+        } else {
+#pragma unroll
+            for (int k = 0; k < V; ++k) { bg[k] = bias[c + k]; bu[k] = bias[inter + c + k]; }
+        }
+    }
 #pragma unroll
     for (int k = 0; k < V; ++k) {
-        const float gg = fminf(g[k] * rs + (bias ? bias[c + k] : 0.f), limit);
-        const float uu = fminf(fmaxf(u[k] * rs + (bias ? bias[inter + c + k] : 0.f), -limit), limit);
+        const float gg = fminf(g[k] * rs + bg[k], limit);
+        const float uu = fminf(fmaxf(u[k] * rs + bu[k], -limit), limit);
         o[k] = gg / (1.0f + expf(-slope * gg)) * (uu + shift);
     }
     NiVec16<T>::store(out + (size_t)t * inter + c, o);

@@ -13,6 +13,11 @@
     python -m nanoinfer_b200.kernels.microbench lightning --batch 1 --tokens 2048 --heads 16 --dim 128 --vdim 128
     python -m nanoinfer_b200.kernels.microbench qk_norm_rope --batch 1 --tokens 2048 --heads 16 --kv-heads 8 --dim 128
     python -m nanoinfer_b200.kernels.microbench routed --tokens 8 --experts 16 --identity 0 --top 3 --sigmoid --on-input --shared-ff 2048
+    python -m nanoinfer_b200.kernels.microbench attention_prefill --tokens 2048 --q-heads 16 --head-dim 128 --sink --chunk 1024
+    python -m nanoinfer_b200.kernels.microbench attention_decode --batch 8 --context 2048 --q-heads 16 --head-dim 128 --sink
+    python -m nanoinfer_b200.kernels.microbench lightning --batch 1 --tokens 2048 --heads 8 --dim 128 --vdim 128 --retention
+    python -m nanoinfer_b200.kernels.microbench qk_norm_rope --batch 1 --tokens 2048 --heads 16 --kv-heads 8 --dim 128 --head-unit
+    python -m nanoinfer_b200.kernels.microbench capped_unit --rows 2048 --ff 8192 --width 2048
 
 Each case runs its kernel over several distinct copies of its inputs in turn (together
 larger than the L2 cache, so every run reads from HBM), times it with CUDA events after
@@ -211,10 +216,12 @@ def attention_decode(args) -> None:
         scratch = torch.empty(b * hq * splits * (hd + 2), dtype=torch.float32, device=DEV)
         fns = [lambda kc=kc, vc=vc: ops.attention_decode(q, kc, vc, out, None, b, positions, seq_of, table, hq, hkv, hd,
                                                          page, None, 1.0 / math.sqrt(hd), splits, scratch, tickets,
-                                                         score_cap=args.score_cap)
+                                                         score_cap=args.score_cap, chunk=args.chunk, sink=args.sink)
                for kc, vc in caches]
     us = _time(fns, args.iters)
-    print(f"attention_decode{' (merge through scratch)' if args.scratch_merge else ''}{' (balanced)' if args.balanced else ''}{' ragged' if args.ragged else ''} batch={b} context={ctx} heads={hq}/{hkv} hd={hd} page={page} splits={splits}: "
+    if args.chunk:           # only the keys of the last token's own chunk are read
+        kv_bytes = kv_bytes * ((ctx - 1) % args.chunk + 1) // ctx
+    print(f"attention_decode{' with a sink' if args.sink else ''}{f' chunks of {args.chunk}' if args.chunk else ''}{' (merge through scratch)' if args.scratch_merge else ''}{' (balanced)' if args.balanced else ''}{' ragged' if args.ragged else ''} batch={b} context={ctx} heads={hq}/{hkv} hd={hd} page={page} splits={splits}: "
           f"{us:.2f} us, {kv_bytes / us / 1e3:.0f} GB/s of cache")
 
 
@@ -233,12 +240,14 @@ def attention_prefill(args) -> None:
     cu_q = torch.tensor([0, t], dtype=torch.int32, device=DEV)
     kv_len = torch.tensor([t], dtype=torch.int32, device=DEV)
     fn = lambda: ops.attention_prefill(q, kc, vc, out, tile_seq, tile_row0, len(tiles), cu_q, kv_len, table, hq, hkv,
-                                       hd, page, None, 1.0 / math.sqrt(hd), kernel=args.kernel, score_cap=args.score_cap)
+                                       hd, page, None, 1.0 / math.sqrt(hd), kernel=args.kernel, score_cap=args.score_cap,
+                                       chunk=args.chunk, sink=args.sink)
     us = _time([fn], args.iters)
     ops.check_device_errors()
-    flops = 4.0 * hq * hd * t * (t + 1) / 2
-    print(f"attention_prefill tokens={t} heads={hq}/{hkv} hd={hd} kernel={args.kernel or 'default'}: {us:.1f} us, "
-          f"{flops / us / 1e6:.0f} TFLOP/s (causal)")
+    seen = sum(p % args.chunk + 1 for p in range(t)) if args.chunk else t * (t + 1) / 2       # (query, key) pairs inside the mask
+    flops = 4.0 * hq * hd * seen
+    print(f"attention_prefill{' with a sink' if args.sink else ''}{f' chunks of {args.chunk}' if args.chunk else ''} tokens={t} "
+          f"heads={hq}/{hkv} hd={hd} kernel={args.kernel or 'default'}: {us:.1f} us, {flops / us / 1e6:.0f} TFLOP/s (of the pairs inside the mask)")
 
 
 def decode_step(args) -> None:
@@ -452,6 +461,21 @@ def lightning(args) -> None:
     o = torch.empty(n, H * V, device=DEV)
     y = torch.empty(n, H * V, dtype=bf, device=DEV)
     buf = torch.empty(ops.lightning_max_chunks(n, b) * H * D * V, device=DEV) if t > 1 else None
+    if args.retention:
+        # retention: rotation and key scale give q, k, v in FP32, the recurrence takes them as they are, every head's
+        # read-out is normed on its own and gated by silu
+        pos = torch.arange(t, device=DEV).repeat(b).int()
+        inv_freq = torch.pow(1e6, -2.0 * torch.arange(D // 4, device=DEV) / (D // 2)).float()
+        qkv = torch.empty(n, 2 * H * D + H * V, device=DEV)
+        us_prep = _time([lambda: ops.linear_attention_prepare(proj, pos, inv_freq, D ** -0.5, qkv, H, D, V, D // 2)], args.iters)
+        us_rec = _time([lambda st=st: ops.lightning_recurrence(qkv, st, cu, slots, b, decay, H, D, V, o, max_q_len=t, buf=buf,
+                                                               activation=False) for st in states], args.iters)
+        us_norm = _time([lambda: ops.group_gated_norm(o, proj, 2 * H * D + H * V, None, 1e-6, y, V, gate="silu")], args.iters)
+        print(f"retention batch={b} tokens={t} heads={H} dim={D} vdim={V}: rotation and key scale {us_prep:.2f} us "
+              f"({n * (2 * H * D + H * V) * (2 + 4) / us_prep / 1e3:.0f} GB/s), recurrence on FP32 q, k, v {us_rec:.2f} us "
+              f"({2 * b * H * D * V * 4 / us_rec / 1e3:.0f} GB/s of state, {4.0 * n * H * D * V / us_rec / 1e6:.2f} TFLOP/s FP32), "
+              f"per-head gated norm {us_norm:.2f} us ({n * H * V * (4 + 2 + 2) / us_norm / 1e3:.0f} GB/s)")
+        return
     us_rec = _time([lambda st=st: ops.lightning_recurrence(proj, st, cu, slots, b, decay, H, D, V, o, max_q_len=t, buf=buf) for st in states], args.iters)
     us_norm = _time([lambda: ops.lightning_gated_norm(o, proj, 2 * H * D + H * V, norm_w, 1e-6, y)], args.iters)
     state_bytes = 2 * b * H * D * V * 4                      # S read and written once per step
@@ -482,10 +506,38 @@ def qk_norm_rope(args) -> None:
     seq = torch.repeat_interleave(torch.arange(b, device=DEV), t).int()
     inv_freq = torch.pow(500000.0, -2.0 * torch.arange(D // 4, device=DEV) / (D // 2)).float()
     q = torch.empty(n, H * D, dtype=bf, device=DEV)
-    us = _time([lambda p=p: ops.qk_norm_rope(p, bias, qg, kg, 1e-6, pos, seq, table, inv_freq, 1.2, q, k_pages, v_pages, H, G, D, D,
-                                             D // 2, page) for p in projs], args.iters)
+    if args.head_unit:       # no bias, no whole-projection norms; the whole head rotated, then every head normed on its own
+        inv_full = torch.pow(500000.0, -2.0 * torch.arange(D // 2, device=DEV) / D).float()
+        us = _time([lambda p=p: ops.qk_norm_rope(p, None, None, None, 1e-6, pos, seq, table, inv_full, 1.0, q, k_pages, v_pages, H, G, D, D,
+                                                 D, page, head_unit=True) for p in projs], args.iters)
+    else:
+        us = _time([lambda p=p: ops.qk_norm_rope(p, bias, qg, kg, 1e-6, pos, seq, table, inv_freq, 1.2, q, k_pages, v_pages, H, G, D, D,
+                                                 D // 2, page) for p in projs], args.iters)
     moved = n * cols * 2 * 2                              # every column read once and written once
-    print(f"qk_norm_rope batch={b} tokens={t} heads={H}/{G} dim={D}: {us:.2f} us ({moved / us / 1e3:.0f} GB/s)")
+    print(f"qk_norm_rope{' (rotation, then a norm per head)' if args.head_unit else ''} batch={b} tokens={t} heads={H}/{G} dim={D}: "
+          f"{us:.2f} us ({moved / us / 1e3:.0f} GB/s)")
+
+
+def capped_unit(args) -> None:
+    """The row-wise kernels of a biased capped unit inside a layer that norms its sublayers' outputs: the activation
+    (gate and up biases before the caps) on [rows, 2 ff], and the normed addition of an FP32 [rows, width] output (with
+    the down projection's bias) that also leaves the stream's bfloat16 copy."""
+    n, f, d = args.rows, args.ff, args.width
+    bf = torch.bfloat16
+    g = torch.Generator(device=DEV).manual_seed(0)
+    copies = max(2, min(32, -(-2 * L2_BYTES // (n * 2 * f * 2))))
+    gus = [torch.randn(n, 2 * f, device=DEV, generator=g).to(bf) for _ in range(copies)]
+    bias = torch.randn(2 * f, device=DEV, generator=g)
+    act = torch.empty(n, f, dtype=bf, device=DEV)
+    us_act = _time([lambda x=x: ops.capped_glu(x, act, 7.0, 1.702, 1.0, bias=bias) for x in gus], args.iters)
+    copies = max(2, min(32, -(-2 * L2_BYTES // (n * d * 4))))
+    ys = [torch.randn(n, d, device=DEV, generator=g) for _ in range(copies)]
+    hs = [torch.randn(n, d, device=DEV, generator=g) for _ in range(copies)]
+    w, b = torch.ones(d, device=DEV), torch.randn(d, device=DEV, generator=g)
+    r = torch.empty(n, d, dtype=bf, device=DEV)
+    us_add = _time([lambda y=y, h=h: ops.add_normed(h, y, w, 1e-6, bias=b, rounded=r) for y, h in zip(ys, hs)], args.iters)
+    print(f"capped_unit rows={n} ff={f} width={d}: activation with biases {us_act:.2f} us ({n * f * 6 / us_act / 1e3:.0f} GB/s), "
+          f"normed addition with bias and bfloat16 copy {us_add:.2f} us ({n * d * 14 / us_add / 1e3:.0f} GB/s)")
 
 
 def routed(args) -> None:
@@ -627,6 +679,8 @@ def main() -> None:
         p.add_argument("--splits", type=int, default=0)
         p.add_argument("--kernel", default=None, choices=["tc", "mma"], help="prefill: insist on one kernel")
         p.add_argument("--score-cap", type=float, default=0.0, help="bound the scaled scores by cap * tanh(s / cap)")
+        p.add_argument("--chunk", type=int, default=0, help="a token sees only the keys of its own chunk of this many positions")
+        p.add_argument("--sink", action="store_true", help="one is added to the softmax's denominator")
         p.add_argument("--copies", type=int, default=0, help="decode: cache copies used in turn (default: enough to exceed L2; 1: the cache stays in L2)")
         p.add_argument("--balanced", action="store_true", help="decode: the kernel that deals the keys evenly over a fixed grid")
         p.add_argument("--ragged", action="store_true", help="decode: contexts from a quarter of --context up to it")
@@ -650,6 +704,7 @@ def main() -> None:
     p.add_argument("--heads", type=int, default=16)
     p.add_argument("--dim", type=int, default=128)
     p.add_argument("--vdim", type=int, default=128)
+    p.add_argument("--retention", action="store_true", help="rotated queries and keys in FP32, no activations, a norm per head, a silu gate")
     p.set_defaults(fn=lightning)
     p = sub.add_parser("qk_norm_rope")
     p.add_argument("--batch", type=int, default=1)
@@ -658,7 +713,13 @@ def main() -> None:
     p.add_argument("--heads", type=int, default=16)
     p.add_argument("--kv-heads", type=int, default=8)
     p.add_argument("--dim", type=int, default=128)
+    p.add_argument("--head-unit", action="store_true", help="no bias and no whole-projection norm; every head normed on its own after the rotation")
     p.set_defaults(fn=qk_norm_rope)
+    p = sub.add_parser("capped_unit")
+    p.add_argument("--rows", type=int, default=2048)
+    p.add_argument("--ff", type=int, default=8192)
+    p.add_argument("--width", type=int, default=2048)
+    p.set_defaults(fn=capped_unit)
     p = sub.add_parser("routed")
     p.add_argument("--tokens", type=int, default=2048)
     p.add_argument("--width", type=int, default=2048)

@@ -61,6 +61,7 @@ _SIGNATURES = {
     "lightning": {
         "ni_lightning_recurrence": [_P, _I, _I, _P, _LL, _P, _P, _P, _P, _I, _I, _I, _P, _LL, _I, _I, _I, _I, _P],
         "ni_linear_attention_prepare": [_P, _I, _I, _P, _P, _F, _P, _I, _I, _I, _I, _I, _P],
+        "ni_retention_token_step": [_P, _I, _I, _P, _LL, _P, _P, _P, _P, _I, _I, _I, _I, _P, _P, _I, _F, _P],
         "ni_group_gated_norm": [_P, _P, _I, _I, _I, _P, _F, _P, _I, _I, _I, _I, _P],
         "ni_lightning_max_chunks": [_I, _I],
         "ni_lightning_gated_norm": [_P, _P, _I, _I, _I, _P, _F, _P, _I, _I, _P],
@@ -714,6 +715,22 @@ def linear_attention_prepare(proj, positions, inv_freq, k_scale, qkv, n_heads, d
         int(rotary_dim), _stream()), "linear_attention_prepare")
 
 
+def retention_token_step(proj, state, cu_q, slots, n_seqs, decay, n_heads, dim, vdim, out, positions, inv_freq, rotary_dim,
+                         k_scale) -> None:
+    """A step in which every request brings ONE token, for a retention layer, in one launch: q and k of proj's columns
+    (q | k | v | ...) are rotated (as linear_attention_prepare does) and k scaled, then S <- decay_h S + k v^T and
+    out = S^T q as in lightning_recurrence with ``activation`` False."""
+    n = proj.shape[0]
+    if n != n_seqs or proj.shape[1] < n_heads * (2 * dim + vdim) or out.shape != (n, n_heads * vdim) or \
+            decay.numel() != n_heads or state.shape[1] < n_heads * dim * vdim or (rotary_dim > 0 and inv_freq.numel() != rotary_dim // 2):
+        raise KernelError("retention_token_step: shapes do not agree (one token per request)")
+    _check(load("lightning").ni_retention_token_step(
+        _dev(proj, "proj"), _code(proj, "proj"), proj.shape[1], _dev(state, "state", torch.float32), state.shape[1],
+        _dev(cu_q, "cu_q", torch.int32), _dev(slots, "slots", torch.int32), _dev(decay, "decay", torch.float32),
+        _dev(out, "out", torch.float32), n_seqs, n_heads, dim, vdim, _dev(positions, "positions", torch.int32),
+        _dev(inv_freq, "inv_freq", torch.float32), int(rotary_dim), float(k_scale), _stream()), "retention_token_step")
+
+
 def group_gated_norm(o, proj, col0, weight, eps, y, group: int, gate: str = "sigmoid") -> None:
     """y = o / sqrt(mean over each group of ``group`` neighbouring columns of o^2 + eps) * weight * act(proj[:, col0 :
     col0 + N]); o float32 [T, N], weight float32 [N] or None (1), y [T, N] of proj's dtype; ``gate`` "sigmoid" or "silu"."""
@@ -1354,10 +1371,12 @@ def attention_decode_cluster_merge(on: bool) -> None:
 
 def attention_decode(q, k_pages, v_pages, out, token_list, n_items, positions, seq_of_token, block_table,
                      n_q_heads, n_kv_heads, head_dim, page_size, window, scale, n_splits, scratch,
-                     tickets, warm=(), score_cap: float = 0.0, chunk: int = 0, sink: bool = False) -> None:
+                     tickets, warm=(), score_cap: float = 0.0, chunk: int = 0, sink: bool = False,
+                     shared_pages: bool = False) -> None:
     """Split-K attention of single query tokens (bfloat16).  ``score_cap`` c > 0 bounds the scaled scores:
     s <- c * tanh(s / c).  ``chunk`` c > 0: the token at position p sees only the keys from p - p % c on; ``sink``: one
-    is added to the softmax's denominator.  ``token_list`` int32 [n_items] or
+    is added to the softmax's denominator.  ``shared_pages``: the pages hold ONE head that all ``n_kv_heads`` of the
+    call read (more than 16 query heads over one shared head, dealt over groups of at most 16).  ``token_list`` int32 [n_items] or
     None for tokens 0..n_items-1.  scratch: float32, at least n_items * Hq * n_splits *
     (head_dim + 2); tickets: int32 zeros, at least n_items * Hkv (left zero by the kernel).
     ``warm``: up to two (tensor, first byte, bytes) (weights that the kernels after it read): the
@@ -1369,7 +1388,9 @@ def attention_decode(q, k_pages, v_pages, out, token_list, n_items, positions, s
         raise KernelError("attention_decode: scratch or tickets too small")
     lib = load("attention_decode")
     capped = score_cap and score_cap > 0.0
-    if chunk or sink:
+    if shared_pages and k_pages.shape[1] != 1:
+        raise KernelError("attention_decode: shared pages hold one head")
+    if chunk or sink or shared_pages:
         _check(lib.ni_attention_decode_masked(
             _dev(q, "q", torch.bfloat16), _dev(k_pages, "k_pages", torch.bfloat16),
             _dev(v_pages, "v_pages", torch.bfloat16), _dev(out, "out", torch.bfloat16),
@@ -1377,7 +1398,8 @@ def attention_decode(q, k_pages, v_pages, out, token_list, n_items, positions, s
             _dev(positions, "positions", torch.int32), _dev(seq_of_token, "seq_of_token", torch.int32),
             _dev(block_table, "block_table", torch.int32), block_table.shape[1], n_q_heads, n_kv_heads,
             head_dim, page_size, int(window) if window else 0, float(scale), float(score_cap or 0.0), int(chunk or 0),
-            1 if sink else 0, n_splits, _dev(scratch, "scratch", torch.float32), _dev(tickets, "tickets", torch.int32),
+            (1 if sink else 0) | (2 if shared_pages else 0), n_splits, _dev(scratch, "scratch", torch.float32),
+            _dev(tickets, "tickets", torch.int32),
             *regions, _stream()), "attention_decode")
         return
     _check((lib.ni_attention_decode_capped if capped else lib.ni_attention_decode)(

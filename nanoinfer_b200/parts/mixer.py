@@ -73,13 +73,20 @@ class PagedAttendMixin:
             ops.attention_generic(q, cache.k_pages, cache.v_pages, att, ctx.positions, ctx.seq_of_token,
                                   table, *common, head_slopes=slopes, score_cap=cap, chunk=chunk, sink=sink)
             return
-        decode_ok = self.head_dim in ops.DECODE_HEAD_DIMS and self.n_heads // self.n_kv <= 16
+        # The single-token kernels take up to 16 query heads per kv head.  More heads over ONE shared head (a compressed
+        # cache) are dealt over several groups that all read the pages' one head.
+        n_kv, shared = self.n_kv, False
+        if self.n_kv == 1 and self.n_heads > 16:
+            groups = next((g for g in range(2, self.n_heads + 1) if self.n_heads % g == 0 and self.n_heads // g <= 16), None)
+            if groups is not None and cache.k_pages is cache.v_pages:
+                n_kv, shared = groups, True
+        decode_ok = self.head_dim in ops.DECODE_HEAD_DIMS and self.n_heads // n_kv <= 16
         prefill_ok = self.head_dim % 16 == 0 and self.head_dim <= ops.PREFILL_MAX_HEAD_DIM
         plan = None if ctx.decode_only else ctx.plan_of(self)    # a step of single tokens needs no lists
         n_dec = n if plan is None else plan.scalars["n_dec"]
         dec_list = None if plan is None else plan.arrays["dec_tokens"]
         if n_dec > 0:
-            if (decode_ok and cap == 0.0 and chunk == 0 and not sink and rt.balanced_attention(n_dec, self.n_kv, self.head_dim)
+            if (decode_ok and cap == 0.0 and chunk == 0 and not sink and not shared and rt.balanced_attention(n_dec, self.n_kv, self.head_dim)
                     and n_dec <= ops.DECODE_BALANCED_MAX_ITEMS):
                 # many tokens: their keys dealt evenly over a fixed set of blocks, whatever their lengths
                 scratch = rt.workspace("attention_decode_balanced_partials",
@@ -89,13 +96,14 @@ class PagedAttendMixin:
                                               ctx.seq_of_token, table, *common, scratch, tickets,
                                               warm=rt.warm_attention(self.w_o, ctx))
             elif decode_ok:
-                splits = ops.decode_splits(n_dec, self.n_kv, self.head_dim, ctx.max_kv_len)
+                splits = ops.decode_splits(n_dec, n_kv, self.head_dim, ctx.max_kv_len)
                 scratch = rt.workspace("attention_decode_partials",
                                        n_dec * self.n_heads * splits * (self.head_dim + 2), torch.float32)
-                tickets = rt.workspace("attention_decode_tickets", n_dec * self.n_kv, torch.int32, zero=True)
+                tickets = rt.workspace("attention_decode_tickets", n_dec * n_kv, torch.int32, zero=True)
                 ops.attention_decode(q, cache.k_pages, cache.v_pages, att, dec_list, n_dec, ctx.positions,
-                                     ctx.seq_of_token, table, *common, splits, scratch, tickets,
-                                     warm=rt.warm_attention(self.w_o, ctx), score_cap=cap, chunk=chunk, sink=sink)
+                                     ctx.seq_of_token, table, self.n_heads, n_kv, *common[2:], splits, scratch, tickets,
+                                     warm=rt.warm_attention(self.w_o, ctx), score_cap=cap, chunk=chunk, sink=sink,
+                                     shared_pages=shared)
             else:
                 ops.attention_generic(q, cache.k_pages, cache.v_pages, att, ctx.positions, ctx.seq_of_token,
                                       table, *common, token_list=dec_list, score_cap=cap, chunk=chunk, sink=sink)

@@ -266,15 +266,18 @@ class Retention(Part):
         n = proj.shape[0]
         h, d, v = self.H, self.D, self.V
         f32 = torch.float32
-        qkv = rt.empty(n, self.gate_col, dtype=f32)
-        ops.linear_attention_prepare(proj, ctx.positions, self.position.inv_freq, self.key_scale, qkv, h, d, v,
-                                     self.position.rotary_dim)
         o = rt.empty(n, h * v, dtype=f32)
-        buf = None
-        if ctx.max_q_len > 1:       # chunks: every chunk's own sum, then the state before it (one buffer for all layers)
+        if ctx.max_q_len == 1:      # single tokens: rotation, key scale, state update and read-out in one launch
+            ops.retention_token_step(proj, cache.state, ctx.cu_q, ctx.slots, ctx.n_seqs, self.decay, h, d, v, o,
+                                     ctx.positions, self.position.inv_freq, self.position.rotary_dim, self.key_scale)
+        else:
+            qkv = rt.empty(n, self.gate_col, dtype=f32)
+            ops.linear_attention_prepare(proj, ctx.positions, self.position.inv_freq, self.key_scale, qkv, h, d, v,
+                                         self.position.rotary_dim)
+            # chunks: every chunk's own sum, then the state before it (one buffer for all layers)
             buf = rt.workspace("lightning_chunks", ops.lightning_max_chunks(n, ctx.n_seqs) * h * d * v, f32)
-        ops.lightning_recurrence(qkv, cache.state, ctx.cu_q, ctx.slots, ctx.n_seqs, self.decay, h, d, v, o,
-                                 max_q_len=ctx.max_q_len, buf=buf, activation=False)
+            ops.lightning_recurrence(qkv, cache.state, ctx.cu_q, ctx.slots, ctx.n_seqs, self.decay, h, d, v, o,
+                                     max_q_len=ctx.max_q_len, buf=buf, activation=False)
         y = rt.empty(n, h * v)
         ops.group_gated_norm(o, proj, self.gate_col, None, self.eps, y, v, gate="silu")
         return rt.linear(y, self.w_o, out_dtype=f32, residual=residual)

@@ -365,6 +365,21 @@ def test_retention_state_keeps_a_far_token(tmp_path, dtype, H, D, V, decay, rot)
     _follow(d, dtype, {"same": base, "other": other}, want, [0, 63, 64, 129, 250, 256, 257, 272, 290] + list(range(291, n + 1)))
 
 
+@pytest.mark.parametrize("heads", [24, 34, 17])
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_many_latent_heads_over_one_cache_row(tmp_path, dtype, heads):
+    """More query heads than one block of the single-token kernel takes (16): 24 and 34 heads are dealt over two groups
+    that read the same cache row of 96 + 32 numbers, 17 (a prime) go the plain way; prompt portions and single tokens."""
+    layer = tm.latent(heads, 8, 32, 8, 96, 40, 5000.0, 0.3, None)
+    d = str(tmp_path / "m")
+    tm.write_model(d, _one_layer(layer, width=48), heads)
+    cfg, w = load_plain(d)
+    reqs = {"a": random_tokens(120, 70, 1), "b": random_tokens(120, 45, 2)}
+    want = {rid: whole_sequence(cfg, w, toks).float() for rid, toks in reqs.items()}
+    steps = ru.tail_by_token(reqs, tail=24)
+    _compare(ru.run_trace(_runner(d, dtype, steps), steps), want, dtype, f"{heads} latent heads")
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_first_tokens_and_short_portions(models, dtype):
     """Portions of two tokens from the sequence's start on, next to a request that starts with a single token."""
