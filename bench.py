@@ -444,7 +444,7 @@ def mobatar_config(z):
     """As many layer runs as the Llama model has layers, in the order attention with a sink, side-by-side layer,
     latent attention, side-by-side layer; the last quarter of the runs use the weights of the first quarter.  Heads
     of 128 throughout: the sink attention and the chunk-masked side (chunks of 1,024 positions) have the Llama
-    model's head counts, retention half as many heads of 128 x 128, the latent row is 96 + 32 wide under a window of
+    model's head counts, retention half as many heads of 128 x 128, the latent row is 112 + 16 wide under a window of
     1,024.  The dense unit has the Llama model's three matrices (plus biases)."""
     heads, n = z["width"] // 128, z["layers"]
     mlp = {"kind": "dense", "ff": z["ff"], "limit": 7.0}
@@ -457,20 +457,20 @@ def mobatar_config(z):
                               "rot": {"dims": 128, "base": 500000.0, "scaling": llama3}}}
         if i % 4 == 2:
             return {"type": "latent_attention", "mlp": mlp,
-                    "mixer": {"heads": heads, "dim": 64, "rot_dim": 32, "vdim": 128, "kv_rank": 96, "scale": 96 ** -0.5,
-                              "rot": {"dims": 32, "base": 500000.0}, "mask": {"size": 1024}}}
+                    "mixer": {"heads": heads, "dim": 64, "rot_dim": 16, "vdim": 128, "kv_rank": 112, "scale": 80 ** -0.5,
+                              "rot": {"dims": 16, "base": 500000.0}, "mask": {"size": 1024}}}
         left = {"heads": heads, "kv_heads": z["kv_heads"], "dim": 128, "vdim": 128, "scale": 128 ** -0.5, "mask": {"size": 1024},
-                "rot": {"dims": 128, "base": 500000.0, "scaling": {"factor": 4.0}}}
+                "rot": {"dims": 128, "base": 500000.0, "scaling": {"factor": 2.0}}}
         n_right = max(heads // 2, 1)
-        right = {"heads": n_right, "dim": 128, "vdim": 128, "rot": {"dims": 64, "base": 1000000.0},
+        right = {"heads": n_right, "dim": 128, "vdim": 128, "rot": {"dims": 64, "base": 100000.0},
                  "decay": [1.0 - 2.0 ** -(5 + 5 * h / max(n_right - 1, 1)) for h in range(n_right)]}
-        return {"type": "parallel", "mlp": mlp, "mixer": {"left": left, "right": right, "left_scale": 1.2, "right_scale": 0.9}}
+        return {"type": "parallel", "mlp": mlp, "mixer": {"left": left, "right": right, "left_scale": 1.1, "right_scale": 0.8}}
 
     layers = [layer(i) for i in range(n)]
     for i in range(n - n // 4, n):
         layers[i] = dict(layers[i - (n - n // 4)], weights_of=i - (n - n // 4))
     return {"architecture": "Mobatar", "vocab": z["vocab"], "width": z["width"], "norm": {"eps": 1e-6},
-            "embedding": {"bigram": {"buckets": 8191, "mul_prev": 127, "mul_cur": 17}}, "layers": layers}
+            "embedding": {"bigram": {"buckets": 8191, "mul_prev": 31, "mul_cur": 7}}, "layers": layers}
 
 
 DESIGN_CONFIGS = {"runevik": runevik_config, "vuvalorn": vuvalorn_config, "tazulix": tazulix_config, "mobatar": mobatar_config}

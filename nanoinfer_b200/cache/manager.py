@@ -5,7 +5,7 @@ A *group* is a set of layer runs with the same need (KV head count, head size, w
 Each group has a page pool and, per request, a block table of its own; a page id means
 the same slot in the K and V tensors of every run of that group.  Pages are taken on
 demand, portion by portion (``append``), given back when the request ends (``free``) and,
-in a windowed group, as soon as the window has passed them (``release_passed``).  A
+in a group with a window or with chunks, as soon as no later query can see them (``release_passed``).  A
 request also holds one *slot*: the row of its block tables in the host mirror that the
 step function uploads, and the row of every per-request state tensor.
 
@@ -32,10 +32,13 @@ from .page_pool import OutOfPages, PagePoolError
 
 @dataclass(frozen=True)
 class GroupSpec:
-    """What the runs of one cache group share."""
+    """What the runs of one cache group share.  ``window``: a query sees the last ``window`` keys; ``chunk``: it sees
+    the keys of its own chunk of ``chunk`` positions (chunks counted from position 0); neither: all keys.  Pages that
+    no later query can see are given back while the request runs."""
     num_kv_heads: int
     head_dim: int
     window: Optional[int] = None
+    chunk: Optional[int] = None
 
 
 class CacheError(RuntimeError):
@@ -77,13 +80,19 @@ class CacheManager:
         self._lib = lib = native.lib()
         n = len(self.groups)
         pages = (ctypes.c_int32 * n)(*[int(p) for p in pages_per_group])
-        windows = (ctypes.c_int32 * n)(*[-1 if g.window is None else int(g.window) for g in self.groups])
+        if any(g.window is not None and g.chunk is not None for g in self.groups):
+            raise ValueError("a cache group has a window or chunks, not both")
+        if any(g.chunk is not None and g.chunk < 1 for g in self.groups):
+            raise ValueError("a chunk has at least one position")
+        # the compiled side takes one number per group: w >= 0 a window, -1 all keys, -(c + 1) chunks of c positions
+        windows = (ctypes.c_int32 * n)(*[int(g.window) if g.window is not None else (-(int(g.chunk) + 1) if g.chunk is not None else -1)
+                                         for g in self.groups])
         self._h = lib.ni_cache_create(n, pages, windows, page_size, max_requests, max_tokens_per_request)
         if not self._h:
             raise ValueError("the cache manager could not be created from these sizes")
         self.table_width = lib.ni_cache_table_width(self._h)
         self.pools = [_PoolView(lib, self._h, g) for g in range(n)]
-        self._windowed = any(g.window is not None for g in self.groups)
+        self._windowed = any(g.window is not None or g.chunk is not None for g in self.groups)
         # the compiled manager's mirror of the block tables, one row per slot; -1 = no page
         self.mirror = [np.ctypeslib.as_array(lib.ni_cache_mirror(self._h, g), shape=(max_requests, self.table_width))
                        for g in range(n)]

@@ -92,7 +92,8 @@ struct Held {
 
 struct CacheManager {
     int page_size, max_requests, max_tokens, table_width;
-    std::vector<int> windows;                      // per group, -1 = all keys
+    std::vector<int> windows;                      // per group: w >= 0 the last w keys; -1 all keys; -(c + 1), c >= 1: the keys of
+                                                   // the query's own chunk of c positions (chunks counted from position 0)
     std::vector<PagePool> pools;
     std::vector<std::vector<int32_t>> mirror;      // per group [max_requests * table_width], -1 = no page
     std::vector<int> free_slots;
@@ -105,7 +106,7 @@ struct CacheManager {
         : page_size(page), max_requests(max_req), max_tokens(max_tok), table_width((max_tok + page - 1) / page) {
         for (int g = 0; g < n_groups; ++g) {
             windows.push_back(win[g]);
-            windowed = windowed || win[g] >= 0;
+            windowed = windowed || win[g] != -1;
             pools.emplace_back(pages[g]);
             mirror.emplace_back((size_t)max_req * table_width, -1);
         }
@@ -172,7 +173,11 @@ struct CacheManager {
     }
     int first_needed_page(int g, int length) const {   // first page a query at position >= length can still see
         const int w = windows[(size_t)g];
-        if (w < 0) return 0;
+        if (w == -1) return 0;
+        if (w < -1) {                                  // chunks: the next query's chunk begins at length - length % c
+            const int c = -w - 1;
+            return (length - length % c) / page_size;
+        }
         const int lo = length - w + 1;
         return (lo > 0 ? lo : 0) / page_size;
     }
@@ -182,7 +187,7 @@ struct CacheManager {
         if (!h) return kErrArgument;
         int released = 0;
         for (int g = 0; g < n_groups(); ++g) {
-            if (windows[(size_t)g] < 0) continue;
+            if (windows[(size_t)g] == -1) continue;
             auto& table = h->tables[(size_t)g];
             int first = first_needed_page(g, h->length);
             if (first > (int)table.size()) first = (int)table.size();
@@ -263,7 +268,7 @@ NI_HOST_EXPORT int ni_pool_give_back(void* p, const int32_t* pages, int n) { ret
 NI_HOST_EXPORT const char* ni_pool_last_error(void* p) { return static_cast<PagePool*>(p)->error.c_str(); }
 
 // ---- cache manager -------------------------------------------------------------------------------
-// windows[g] < 0: the group keeps all keys.
+// windows[g] == -1: the group keeps all keys; w >= 0: the last w; -(c + 1): those of the running chunk of c positions.
 NI_HOST_EXPORT void* ni_cache_create(int n_groups, const int* pages_per_group, const int* windows, int page_size,
                                      int max_requests, int max_tokens_per_request) {
     if (n_groups <= 0 || page_size <= 0 || max_requests <= 0 || max_tokens_per_request <= 0) return nullptr;

@@ -247,11 +247,11 @@ class ModelRunner:
                 if isinstance(one, (PagedKVNeed, PagedNeed)):
                     if self.caches[r].group >= 0:
                         raise StepError(f"run {r}: more than one paged cache need")
-                    key = (planes_of(one), one.window)
+                    key = (planes_of(one), one.window, one.chunk)
                     if key not in group_keys:
                         group_keys.append(key)
                         kv = isinstance(one, PagedKVNeed)
-                        group_specs.append(GroupSpec(one.num_kv_heads if kv else 0, one.head_dim if kv else 0, one.window))
+                        group_specs.append(GroupSpec(one.num_kv_heads if kv else 0, one.head_dim if kv else 0, one.window, one.chunk))
                     self.caches[r].group = group_keys.index(key)
                 elif isinstance(one, StateNeed):
                     if r in self._state_runs:

@@ -465,7 +465,7 @@ def lightning(args) -> None:
         # retention: rotation and key scale give q, k, v in FP32, the recurrence takes them as they are, every head's
         # read-out is normed on its own and gated by silu
         pos = torch.arange(t, device=DEV).repeat(b).int()
-        inv_freq = torch.pow(1e6, -2.0 * torch.arange(D // 4, device=DEV) / (D // 2)).float()
+        inv_freq = torch.pow(5e5, -2.0 * torch.arange(D // 4, device=DEV) / (D // 2)).float()
         qkv = torch.empty(n, 2 * H * D + H * V, device=DEV)
         us_prep = _time([lambda: ops.linear_attention_prepare(proj, pos, inv_freq, D ** -0.5, qkv, H, D, V, D // 2)], args.iters)
         us_rec = _time([lambda st=st: ops.lightning_recurrence(qkv, st, cu, slots, b, decay, H, D, V, o, max_q_len=t, buf=buf,

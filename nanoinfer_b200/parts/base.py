@@ -72,10 +72,12 @@ class WeightSlot:
 @dataclass(frozen=True)
 class PagedKVNeed:
     """Keys and values of every token, in pages; ``window`` = how many most recent
-    tokens stay reachable (None = all)."""
+    tokens stay reachable (None = all); ``chunk`` = c: only the tokens of the running chunk of c positions stay
+    reachable (chunks counted from position 0; not together with a window)."""
     num_kv_heads: int
     head_dim: int
     window: Optional[int] = None
+    chunk: Optional[int] = None
 
 
 @dataclass(frozen=True)
@@ -83,9 +85,10 @@ class PagedNeed:
     """Paged per-token storage of any layout: ``planes`` names each tensor a token has a row in
     and that row's shape, e.g. (("latent", (96,)),) for one compressed vector per token, or keys
     and values of different widths.  The page tensor of a plane with row shape (a, ..., z) is
-    [pages, a, ..., page_size, z].  ``window`` as in PagedKVNeed."""
+    [pages, a, ..., page_size, z].  ``window`` and ``chunk`` as in PagedKVNeed."""
     planes: Tuple[Tuple[str, Tuple[int, ...]], ...]
     window: Optional[int] = None
+    chunk: Optional[int] = None
 
 
 def planes_of(need) -> Tuple[Tuple[str, Tuple[int, ...]], ...]:

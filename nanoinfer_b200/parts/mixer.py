@@ -568,11 +568,11 @@ class NormedQKAttention(PagedAttendMixin, Part):
         self.k_gain = rt.gain(weights["k.norm"]) if qk_norm else None
 
     def cache_need(self):
-        # (a chunked mask keeps all pages: keys before the running chunk are never read again, but nothing gives
-        # them back before the request ends)
+        # with a chunk mask the keys before the running chunk are never read again: the cache gives their pages back
+        chunk = self.chunk or None
         if self.value_dim == self.head_dim:
-            return PagedKVNeed(self.n_kv, self.head_dim, None)
-        return PagedNeed((("k", (self.n_kv, self.head_dim)), ("v", (self.n_kv, self.value_dim))), None)
+            return PagedKVNeed(self.n_kv, self.head_dim, None, chunk)
+        return PagedNeed((("k", (self.n_kv, self.head_dim)), ("v", (self.n_kv, self.value_dim))), None, chunk)
 
     def weights_in_order(self) -> tuple:
         return (self.w_qkv, self.w_o)

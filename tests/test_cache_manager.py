@@ -77,6 +77,31 @@ def test_window_gives_pages_back_early():
     assert cm.pools[0].num_free == 64 and cm.pools[1].num_free == 64
 
 
+@pytest.mark.parametrize("chunk", [10, 4, 7, 1])
+def test_chunks_give_pages_back_at_their_borders(chunk):
+    """A group whose queries see only the keys of their own chunk of ``chunk`` positions keeps the pages from the next
+    query's chunk start on and gives the others back, whatever the portions' sizes."""
+    cm = CacheManager([GroupSpec(1, 16, None), GroupSpec(1, 16, None, chunk)], [64, 64], page_size=4,
+                      max_requests=1, max_tokens_per_request=128)
+    cm.admit("a")
+    peak = 0
+    for step in range(40):
+        cm.append("a", 3)
+        peak = max(peak, cm.pools[1].num_taken)
+        cm.release_passed("a")
+        cm.check_consistency()
+        n = cm.length("a")
+        table = cm.block_table("a", 1)
+        first_needed = (n - n % chunk) // 4              # page of the first key of the chunk that position n falls into
+        assert all(p == -1 for p in table[:first_needed]) and all(p >= 0 for p in table[first_needed:])
+    assert cm.pools[0].num_taken == 30                  # the full group keeps everything
+    assert peak <= -(-(chunk + 3) // 4) + 1             # a chunk and a portion, pages of 4
+    cm.free("a")
+    assert cm.pools[0].num_free == 64 and cm.pools[1].num_free == 64
+    with pytest.raises(ValueError):
+        CacheManager([GroupSpec(1, 16, 8, 8)], [8], page_size=4, max_requests=1, max_tokens_per_request=32)
+
+
 @pytest.mark.parametrize("seed", range(5))
 def test_random_orders_keep_the_books(seed):
     rng = random.Random(seed)

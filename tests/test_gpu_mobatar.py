@@ -369,8 +369,8 @@ def test_retention_state_keeps_a_far_token(tmp_path, dtype, H, D, V, decay, rot)
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_many_latent_heads_over_one_cache_row(tmp_path, dtype, heads):
     """More query heads than one block of the single-token kernel takes (16): 24 and 34 heads are dealt over two groups
-    that read the same cache row of 96 + 32 numbers, 17 (a prime) go the plain way; prompt portions and single tokens."""
-    layer = tm.latent(heads, 8, 32, 8, 96, 40, 5000.0, 0.3, None)
+    that read the same cache row of 112 + 16 numbers, 17 (a prime) go the plain way; prompt portions and single tokens."""
+    layer = tm.latent(heads, 8, 16, 8, 112, 40, 5000.0, 0.3, None)
     d = str(tmp_path / "m")
     tm.write_model(d, _one_layer(layer, width=48), heads)
     cfg, w = load_plain(d)

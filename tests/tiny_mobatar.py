@@ -65,7 +65,7 @@ def again(layer, j):
 
 
 def _m1():
-    a = attention(4, 2, 24, 40, rot(24, 10000.0, llama3(4.0, 64, 1.0, 4.0)), 0.3, dense(136, 1.5))
+    a = attention(4, 2, 24, 40, rot(24, 10000.0, llama3(5.0, 64, 1.0, 3.0)), 0.15, dense(136, 1.5))
     p = side_by_side(chunked(6, 3, 16, 8, rot(16, 50000.0, {"factor": 2.0}), 0.25, 24),
                      retention(3, 20, 12, (0.8, 0.97, 0.999), rot(12, 1000.0)), 1.3, 0.7, dense(72, 2.0))
     la = latent(3, 12, 8, 20, 24, 20, 3000.0, 0.22, None)
@@ -77,8 +77,8 @@ def _m1():
 def _m2():
     a = attention(8, 2, 64, 64, rot(64, 500000.0, llama3(8.0, 128, 1.0, 4.0)), 0.18, dense(192, 2.0))
     p = side_by_side(chunked(4, 1, 128, 128, rot(128, 10000.0, {"factor": 4.0}), 0.09, 48),
-                     retention(2, 64, 64, (0.9, 0.995), rot(64, 100000.0)), 1.2, 0.9, dense(128, 1.0))
-    la = latent(4, 32, 32, 48, 96, 32, 250000.0, 0.15, dense(128, 2.5))
+                     retention(2, 64, 64, (0.9, 0.995), rot(64, 100000.0)), 1.25, 0.85, dense(128, 1.0))
+    la = latent(4, 32, 16, 48, 112, 32, 200000.0, 0.15, dense(128, 2.5))
     return {"architecture": "Mobatar", "vocab": 260, "width": 128, "norm": {"eps": 1e-6},
             "embedding": {"bigram": {"buckets": 64, "mul_prev": 5, "mul_cur": 3}},
             "layers": [p, a, la, again(p, 0)]}
