@@ -23,8 +23,8 @@
 // divides by (sum + 1e-6); this kernel divides by the sum.
 #include "common.cuh"
 
-// Registers per lane for a head: 8 take head sizes up to 256; a second instance with 16 takes up to 512
-// (a compressed cache row can be that wide) and leaves the first one as it was.
+// Registers per lane for a head: 8 take head sizes up to 256; a second instance with 16 takes up to 512 and a third
+// with 32 up to 1,024 (a compressed cache row can be that wide); each leaves the others as they were.
 template <typename T, int ATT_MAX_REGS>
 __global__ void attention_generic_kernel(const T* __restrict__ q, const T* __restrict__ k_pages,
                                          const T* __restrict__ v_pages, T* __restrict__ out,
@@ -104,7 +104,7 @@ NI_EXPORT int ni_attention_generic(const void* q, int dtype, const void* k_pages
     if (n_q_heads <= 0 || n_kv_heads <= 0 || n_q_heads % n_kv_heads || head_dim <= 0 || page_size <= 0 || v_dim < 0 || chunk < 0)
         return NI_ERR_BAD_ARGUMENT;
     if (v_dim == 0) v_dim = head_dim;          // values of the keys' size
-    if (head_dim > 32 * 16 || v_dim > 32 * 16) return NI_ERR_UNSUPPORTED_SIZE;
+    if (head_dim > 32 * 32 || v_dim > 32 * 32) return NI_ERR_UNSUPPORTED_SIZE;
     const int warps = 4;
     const long long items = (long long)n_tokens * n_q_heads;
     const long long blocks = (items + warps - 1) / warps;
@@ -117,7 +117,8 @@ NI_EXPORT int ni_attention_generic(const void* q, int dtype, const void* k_pages
 #define LAUNCH(T)                          \
     do {                                   \
         if (head_dim <= 256 && v_dim <= 256) LAUNCH_R(T, 8); \
-        else LAUNCH_R(T, 16);              \
+        else if (head_dim <= 512 && v_dim <= 512) LAUNCH_R(T, 16); \
+        else LAUNCH_R(T, 32);              \
     } while (0)
     if (dtype == NI_DTYPE_F32) LAUNCH(float);
     else if (dtype == NI_DTYPE_BF16) LAUNCH(__nv_bfloat16);

@@ -351,7 +351,7 @@ def attention_generic(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Ten
                       token_list: Optional[torch.Tensor] = None, head_slopes: Optional[torch.Tensor] = None,
                       score_cap: float = 0.0, value_dim: Optional[int] = None, chunk: int = 0,
                       sink: bool = False) -> None:
-    """The plain attention kernel (any dtype, any head size up to 512).  ``token_list``
+    """The plain attention kernel (any dtype, any head size up to 1,024).  ``token_list``
     int32 [n] restricts it to those tokens of the step.  ``head_slopes`` float32 [Hq] adds
     slope[h] * (key position - query position) to the scaled scores of head h.  ``score_cap`` c > 0
     bounds the scaled scores: s <- c * tanh(s / c).  ``value_dim``: the size of a value where it differs
@@ -365,8 +365,8 @@ def attention_generic(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Ten
         raise KernelError("attention: q must be [T, Hq * head_dim] and out [T, Hq * value_dim]")
     if not (q.dtype == out.dtype == k_pages.dtype == v_pages.dtype):
         raise KernelError("attention: all operands must share one dtype")
-    if head_dim > 512 or v_dim > 512 or v_dim <= 0:
-        raise KernelError(f"attention: head_dim {head_dim} or value_dim {v_dim} beyond 512 is not supported")
+    if head_dim > 1024 or v_dim > 1024 or v_dim <= 0:
+        raise KernelError(f"attention: head_dim {head_dim} or value_dim {v_dim} beyond 1,024 is not supported")
     if k_pages.shape[-1] != head_dim or v_pages.shape[-1] != v_dim:
         raise KernelError("attention: the pages' rows must have the keys' and the values' sizes")
     _check(load("attention_generic").ni_attention_generic(

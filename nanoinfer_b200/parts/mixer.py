@@ -288,9 +288,9 @@ class LatentAttention(PagedAttendMixin, Part):
         Part.__init__(self, spec, hidden_size, weights, rt)
         h, d, v, r, own = self._dims(spec)
         n, gate = self._options(spec)
-        if h <= 0 or d <= 0 or v <= 0 or n < 0 or n % 2 or not 0 < r + n <= 512:
+        if h <= 0 or d <= 0 or v <= 0 or n < 0 or n % 2 or not 0 < r + n <= 1024:
             raise ConfigError(f"latent attention: heads and sizes must be positive, the rotated part even, and the latent "
-                              f"rank with it at most 512 (got {r} + {n})")
+                              f"rank with it at most 1,024 (got {r} + {n})")
         if spec.window is not None and spec.window <= 0:
             raise ConfigError("an attention window must be positive")
         # what the attention kernels see: h query heads over one shared head of size r (+ the rotated key part)

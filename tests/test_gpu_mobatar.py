@@ -381,6 +381,20 @@ def test_many_latent_heads_over_one_cache_row(tmp_path, dtype, heads):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_wide_latent_row(tmp_path, dtype):
+    """A cache row of 560 + 16 numbers: wider than any tensor-core kernel takes, and than the plain kernel's first two
+    instances."""
+    layer = tm.latent(2, 8, 16, 8, 560, 40, 5000.0, 0.3, None)
+    d = str(tmp_path / "m")
+    tm.write_model(d, _one_layer(layer, width=48), 3)
+    cfg, w = load_plain(d)
+    reqs = {"a": random_tokens(120, 60, 1), "b": random_tokens(120, 21, 2)}
+    want = {rid: whole_sequence(cfg, w, toks).float() for rid, toks in reqs.items()}
+    steps = ru.mixed(reqs, tail=5)
+    _compare(ru.run_trace(_runner(d, dtype, steps), steps), want, dtype, "wide latent row")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_first_tokens_and_short_portions(models, dtype):
     """Portions of two tokens from the sequence's start on, next to a request that starts with a single token."""
     d, cfg, reqs, want = models["m1"]

@@ -9,7 +9,8 @@ M2 has sizes the tensor-core attention kernels take (heads of 64 and 128, values
 M3 has values that are 1 or absent elsewhere: one head, one key head per query head, no pair-hash table, no frequency
 scaling, a rotation of the whole head or none, scales of 1, a window of one position and a chunk of two, a latent
 without a rotated part, a retention head that never decays.
-M4 has sizes that are no multiple of 8 anywhere, a chunk and a window that are no multiple of the page.
+M4 has sizes that are no multiple of 8 anywhere, a chunk and a window that are no multiple of the page, and a first
+layer that runs with the weights of a later one.
 """
 import json
 import os
@@ -99,7 +100,7 @@ def _m4():
     la = latent(5, 10, 6, 9, 13, 27, 999.0, 0.27, dense(12, 2.0))
     return {"architecture": "Mobatar", "vocab": 173, "width": 76, "norm": {"eps": 1e-5},
             "embedding": {"bigram": {"buckets": 17, "mul_prev": 1, "mul_cur": 1}},
-            "layers": [la, a, again(la, 0), p]}
+            "layers": [again(la, 2), a, la, p]}                  # the first entry borrows from a LATER layer
 
 
 M1, M2, M3, M4 = _m1(), _m2(), _m3(), _m4()
