@@ -45,28 +45,28 @@ NI_EXPORT int ni_latent_norm_write(const void* proj, int dtype, int ld, int col0
     NI_RETURN_LAUNCH_STATUS();
 }
 
-// x[t, h, :] *= sigmoid(proj[t, col0 + h]);  x [T, H, V]
+// x[t, h, :] *= sigmoid(proj[t, col0 + h]) * scale;  x [T, H, V]
 template <typename T>
 __global__ void head_gate_kernel(T* __restrict__ x, const T* __restrict__ proj, int ld, int col0, int n_tokens, int H,
-                                 int V) {
+                                 int V, float scale) {
     const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= (long long)n_tokens * H * V) return;
     const long long th = idx / V;
     const int t = (int)(th / H), h = (int)(th - (long long)t * H);
-    const float g = 1.0f / (1.0f + expf(-ni_to_float(proj[(size_t)t * ld + col0 + h])));
+    const float g = scale / (1.0f + expf(-ni_to_float(proj[(size_t)t * ld + col0 + h])));
     x[idx] = ni_from_float<T>(ni_to_float(x[idx]) * g);
 }
 
 // The same, 16 bytes per thread (head sizes that are multiples of 8 bfloat16 or 4 float values).
 template <typename T>
 __global__ void head_gate_vec_kernel(T* __restrict__ x, const T* __restrict__ proj, int ld, int col0, long long n_vec, int H,
-                                     int V) {
+                                     int V, float scale) {
     constexpr int N = NiVec16<T>::N;
     const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= n_vec) return;
     const long long th = i / (V / N);
     const int t = (int)(th / H), h = (int)(th - (long long)t * H);
-    const float g = 1.0f / (1.0f + expf(-ni_to_float(proj[(size_t)t * ld + col0 + h])));
+    const float g = scale / (1.0f + expf(-ni_to_float(proj[(size_t)t * ld + col0 + h])));
     float v[N];
     NiVec16<T>::load(x + i * N, v);
 #pragma unroll
@@ -74,7 +74,8 @@ __global__ void head_gate_vec_kernel(T* __restrict__ x, const T* __restrict__ pr
     NiVec16<T>::store(x + i * N, v);
 }
 
-NI_EXPORT int ni_head_gate(void* x, int dtype, const void* proj, int ld, int col0, int n_tokens, int H, int V,
+// scale: one more factor on every gate (1: none) - a mixer whose output is weighted before it is added to another's.
+NI_EXPORT int ni_head_gate(void* x, int dtype, const void* proj, int ld, int col0, int n_tokens, int H, int V, float scale,
                            cudaStream_t stream) {
     if (n_tokens <= 0) return NI_OK;
     if (H <= 0 || V <= 0 || col0 < 0 || col0 + H > ld) return NI_ERR_BAD_ARGUMENT;
@@ -83,19 +84,19 @@ NI_EXPORT int ni_head_gate(void* x, int dtype, const void* proj, int ld, int col
     if (dtype == NI_DTYPE_BF16 && V % 8 == 0) {
         const long long nv = (long long)n_tokens * H * V / 8;
         head_gate_vec_kernel<__nv_bfloat16><<<(int)((nv + 255) / 256), 256, 0, stream>>>(
-            (__nv_bfloat16*)x, (const __nv_bfloat16*)proj, ld, col0, nv, H, V);
+            (__nv_bfloat16*)x, (const __nv_bfloat16*)proj, ld, col0, nv, H, V, scale);
         NI_RETURN_LAUNCH_STATUS();
     }
     if (dtype == NI_DTYPE_F32 && V % 4 == 0) {
         const long long nv = (long long)n_tokens * H * V / 4;
-        head_gate_vec_kernel<float><<<(int)((nv + 255) / 256), 256, 0, stream>>>((float*)x, (const float*)proj, ld, col0, nv, H, V);
+        head_gate_vec_kernel<float><<<(int)((nv + 255) / 256), 256, 0, stream>>>((float*)x, (const float*)proj, ld, col0, nv, H, V, scale);
         NI_RETURN_LAUNCH_STATUS();
     }
     if (dtype == NI_DTYPE_F32)
-        head_gate_kernel<float><<<(int)blocks, 256, 0, stream>>>((float*)x, (const float*)proj, ld, col0, n_tokens, H, V);
+        head_gate_kernel<float><<<(int)blocks, 256, 0, stream>>>((float*)x, (const float*)proj, ld, col0, n_tokens, H, V, scale);
     else if (dtype == NI_DTYPE_BF16)
         head_gate_kernel<__nv_bfloat16><<<(int)blocks, 256, 0, stream>>>((__nv_bfloat16*)x, (const __nv_bfloat16*)proj, ld,
-                                                                        col0, n_tokens, H, V);
+                                                                        col0, n_tokens, H, V, scale);
     else
         return NI_ERR_BAD_ARGUMENT;
     NI_RETURN_LAUNCH_STATUS();

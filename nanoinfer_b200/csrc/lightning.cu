@@ -1065,12 +1065,12 @@ NI_EXPORT int ni_retention_token_step(const void* proj, int dtype, int ld, float
 }
 
 // y[t, g, :] = o[t, g, :] / sqrt(mean(o[t, g, :]^2) + eps) * weight[g, :] * act(gate[t, g, :]) for every group g of V
-// neighbouring columns (weight null: 1); the gate's columns lie in proj at col0; gate_act 0: sigmoid, 1: silu.
-// One block per token, a warp takes a group at a time.
+// neighbouring columns (weight null: 1), times `scale`; the gate's columns lie in proj at col0; gate_act 0: sigmoid,
+// 1: silu.  One block per token, a warp takes a group at a time.
 template <typename T>
 __global__ void group_gated_norm_kernel(const float* __restrict__ o, const T* __restrict__ proj, int ld, int col0,
                                         const float* __restrict__ weight, float eps, T* __restrict__ y, int groups, int V,
-                                        int gate_act) {
+                                        int gate_act, float scale) {
     const int t = blockIdx.x, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
     const float* row = o + (size_t)t * groups * V;
     const T* g = proj + (size_t)t * ld + col0;
@@ -1080,7 +1080,7 @@ __global__ void group_gated_norm_kernel(const float* __restrict__ o, const T* __
         float ss = 0.f;
         for (int i = lane; i < V; i += 32) ss = fmaf(x[i], x[i], ss);
         ss = ni_warp_sum(ss);
-        const float inv = 1.0f / sqrtf(ss / (float)V + eps);
+        const float inv = scale / sqrtf(ss / (float)V + eps);
         for (int i = lane; i < V; i += 32) {
             const int c = grp * V + i;
             const float z = ni_to_float(g[c]);
@@ -1091,17 +1091,18 @@ __global__ void group_gated_norm_kernel(const float* __restrict__ o, const T* __
 }
 
 NI_EXPORT int ni_group_gated_norm(const float* o, const void* proj, int dtype, int ld, int col0, const float* weight,
-                                  float eps, void* y, int n_tokens, int groups, int V, int gate_act, cudaStream_t stream) {
+                                  float eps, void* y, int n_tokens, int groups, int V, int gate_act, float scale,
+                                  cudaStream_t stream) {
     if (n_tokens <= 0) return NI_OK;
     if (groups <= 0 || V <= 0 || col0 < 0 || (long long)col0 + (long long)groups * V > ld || (gate_act != 0 && gate_act != 1))
         return NI_ERR_BAD_ARGUMENT;
     const int threads = groups >= 8 ? 256 : (groups >= 4 ? 128 : 64);
     if (dtype == NI_DTYPE_F32)
         group_gated_norm_kernel<float><<<n_tokens, threads, 0, stream>>>(o, (const float*)proj, ld, col0, weight, eps, (float*)y,
-                                                                         groups, V, gate_act);
+                                                                         groups, V, gate_act, scale);
     else if (dtype == NI_DTYPE_BF16)
         group_gated_norm_kernel<__nv_bfloat16><<<n_tokens, threads, 0, stream>>>(o, (const __nv_bfloat16*)proj, ld, col0, weight,
-                                                                                 eps, (__nv_bfloat16*)y, groups, V, gate_act);
+                                                                                 eps, (__nv_bfloat16*)y, groups, V, gate_act, scale);
     else
         return NI_ERR_BAD_ARGUMENT;
     NI_RETURN_LAUNCH_STATUS();

@@ -62,7 +62,7 @@ _SIGNATURES = {
         "ni_lightning_recurrence": [_P, _I, _I, _P, _LL, _P, _P, _P, _P, _I, _I, _I, _P, _LL, _I, _I, _I, _I, _P],
         "ni_linear_attention_prepare": [_P, _I, _I, _P, _P, _F, _P, _I, _I, _I, _I, _I, _P],
         "ni_retention_token_step": [_P, _I, _I, _P, _LL, _P, _P, _P, _P, _I, _I, _I, _I, _P, _P, _I, _F, _P],
-        "ni_group_gated_norm": [_P, _P, _I, _I, _I, _P, _F, _P, _I, _I, _I, _I, _P],
+        "ni_group_gated_norm": [_P, _P, _I, _I, _I, _P, _F, _P, _I, _I, _I, _I, _F, _P],
         "ni_lightning_max_chunks": [_I, _I],
         "ni_lightning_gated_norm": [_P, _P, _I, _I, _I, _P, _F, _P, _I, _I, _P],
     },
@@ -85,7 +85,7 @@ _SIGNATURES = {
     },
     "latent": {
         "ni_latent_norm_write": [_P, _I, _I, _I, _P, _F, _P, _P, _P, _P, _I, _I, _I, _I, _P],
-        "ni_head_gate": [_P, _I, _P, _I, _I, _I, _I, _I, _P],
+        "ni_head_gate": [_P, _I, _P, _I, _I, _I, _I, _I, _F, _P],
         "ni_latent_rope_write": [_P, _I, _I, _I, _P, _F, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P, _I, _P, _I, _P],
     },
     "gemv_bf16": {
@@ -539,13 +539,13 @@ def latent_rope_write(proj, col0, rank, rot_dim, weight, eps, pages, positions, 
         1 if interleaved else 0, _dev(q, "q"), n_heads, _stream()), "latent_rope_write")
 
 
-def head_gate(x, proj, col0, n_heads, vdim) -> None:
-    """x[t, h, :] *= sigmoid(proj[t, col0 + h]) in place; x [T, H V]."""
+def head_gate(x, proj, col0, n_heads, vdim, scale: float = 1.0) -> None:
+    """x[t, h, :] *= sigmoid(proj[t, col0 + h]) * scale in place; x [T, H V]."""
     n = x.shape[0]
     if x.shape[1] != n_heads * vdim or proj.shape[0] != n or proj.dtype != x.dtype:
         raise KernelError("head_gate: shapes or dtypes do not agree")
     _check(load("latent").ni_head_gate(_dev(x, "x"), _code(x, "x"), _dev(proj, "proj"), proj.shape[1], int(col0), n,
-                                       n_heads, vdim, _stream()), "head_gate")
+                                       n_heads, vdim, float(scale), _stream()), "head_gate")
 
 
 def embedding_scaled(tokens: torch.Tensor, table: torch.Tensor, scale: float, out: torch.Tensor) -> None:
@@ -731,9 +731,10 @@ def retention_token_step(proj, state, cu_q, slots, n_seqs, decay, n_heads, dim, 
         _dev(inv_freq, "inv_freq", torch.float32), int(rotary_dim), float(k_scale), _stream()), "retention_token_step")
 
 
-def group_gated_norm(o, proj, col0, weight, eps, y, group: int, gate: str = "sigmoid") -> None:
-    """y = o / sqrt(mean over each group of ``group`` neighbouring columns of o^2 + eps) * weight * act(proj[:, col0 :
-    col0 + N]); o float32 [T, N], weight float32 [N] or None (1), y [T, N] of proj's dtype; ``gate`` "sigmoid" or "silu"."""
+def group_gated_norm(o, proj, col0, weight, eps, y, group: int, gate: str = "sigmoid", scale: float = 1.0) -> None:
+    """y = scale * o / sqrt(mean over each group of ``group`` neighbouring columns of o^2 + eps) * weight * act(proj[:,
+    col0 : col0 + N]); o float32 [T, N], weight float32 [N] or None (1), y [T, N] of proj's dtype; ``gate`` "sigmoid" or
+    "silu"."""
     n, width = o.shape
     if y.shape != o.shape or y.dtype != proj.dtype or proj.shape[0] != n or group <= 0 or width % group or \
             (weight is not None and weight.numel() != width) or gate not in ("sigmoid", "silu"):
@@ -741,7 +742,7 @@ def group_gated_norm(o, proj, col0, weight, eps, y, group: int, gate: str = "sig
     _check(load("lightning").ni_group_gated_norm(
         _dev(o, "o", torch.float32), _dev(proj, "proj"), _code(proj, "proj"), proj.shape[1], int(col0),
         _dev(weight, "weight", torch.float32) if weight is not None else None, float(eps), _dev(y, "y"), n, width // group,
-        int(group), 1 if gate == "silu" else 0, _stream()), "group_gated_norm")
+        int(group), 1 if gate == "silu" else 0, float(scale), _stream()), "group_gated_norm")
 
 
 def lightning_gated_norm(o, proj, col0, weight, eps, y) -> None:

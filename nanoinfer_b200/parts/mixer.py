@@ -544,6 +544,9 @@ class NormedQKAttention(PagedAttendMixin, Part):
         self.head_unit_norm, self.head_gate = bool(e.get("head_unit_norm", False)), bool(e.get("head_gate", False))
         if self.chunk < 0:
             raise ConfigError("normed-qk attention: a chunk must be a positive number of tokens")
+        # A factor on the mixer's output that whoever owns it may set (mixers side by side weight their outputs): with a
+        # gate per head it rides in the gate, before the output projection, which is linear.
+        self.takes_output_scale, self.output_scale = self.head_gate, 1.0
         if self.head_gate:
             self.kernel_modules = ("latent",)         # the library of csrc that holds the per-head gate
         self.scale = float(spec.softmax_scale)
@@ -609,7 +612,7 @@ class NormedQKAttention(PagedAttendMixin, Part):
             ops.attention_generic(q, cache.k_pages, cache.v_pages, att, ctx.positions, ctx.seq_of_token, table,
                                   h, g, d, rt.page_size, None, self.scale, value_dim=v, chunk=self.chunk, sink=self.sink)
         if self.head_gate:
-            ops.head_gate(att, qkv, self.cols, h, v)
+            ops.head_gate(att, qkv, self.cols, h, v, scale=self.output_scale)
         # the product leaves in FP32 (or is added into the FP32 stream by the kernel itself): the residual sum
         # sees it unrounded
         return rt.linear(att, self.w_o, out_dtype=torch.float32, residual=residual)
@@ -620,7 +623,10 @@ class ParallelMixers(Part):
     specs (``left``, ``right``: MixerSpec of any registered kinds) and the two scales come in the spec's extra; the
     weights of each lie under its side's name ("left.q", "right.o", ...).  Each side keeps what it needs between steps
     in the layer run's one cache view - so at most one of them may need pages, and at most one a state (attention beside
-    a recurrence, say).  The sum is FP32."""
+    a recurrence, say).  The sum is FP32.  Where both sides can carry a factor on their output themselves
+    (``takes_output_scale``) and the second can add its output projection into a given FP32 tensor, the scales ride in
+    the sides' own kernels and the second side's last product adds into the first side's result; otherwise one more
+    kernel forms the weighted sum."""
 
     kernel_modules = ("pointwise",)       # the library of csrc that holds the weighted sum
 
@@ -646,6 +652,11 @@ class ParallelMixers(Part):
             own = {slot[len(name) + 1:]: w for slot, w in weights.items() if slot.startswith(name + ".")}
             self.sub_parts.append(part("mixer", sub.kind)(sub, hidden_size, own, rt))
             self.scales.append(scale)
+        first, second = self.sub_parts
+        self.folded = (all(getattr(p, "takes_output_scale", False) for p in self.sub_parts)
+                       and getattr(second, "adds_into_residual", False))
+        if self.folded:
+            first.output_scale, second.output_scale = self.scales
         safety = [getattr(p, "graph_safe", "none") for p in self.sub_parts]
         self.graph_safe = "all" if all(x == "all" for x in safety) else \
             ("decode" if all(x in ("decode", "all") for x in safety) else "none")
@@ -665,8 +676,17 @@ class ParallelMixers(Part):
         return tuple(w for p in self.sub_parts for w in getattr(p, "weights_in_order", tuple)())
 
     def forward(self, x: torch.Tensor, ctx, cache):
-        left, right = (p.forward(x, ctx, cache) for p in self.sub_parts)
-        if left.dtype != torch.float32 or right.dtype != torch.float32:
+        first, second = self.sub_parts
+        left = first.forward(x, ctx, cache)
+        if left.dtype != torch.float32:
+            raise ConfigError("mixers side by side must hand their outputs over in FP32")
+        if self.folded:
+            right = second.forward(x, ctx, cache, residual=left)       # may add in place and return None
+            if right is not None:
+                ops.residual_add(left, right)
+            return left
+        right = second.forward(x, ctx, cache)
+        if right.dtype != torch.float32:
             raise ConfigError("mixers side by side must hand their outputs over in FP32")
         ops.weighted_sum(left, self.scales[0], right, self.scales[1], left)
         return left

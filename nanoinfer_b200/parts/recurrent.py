@@ -214,6 +214,10 @@ class Retention(Part):
 
     adds_into_residual = True
     graph_safe = "all"
+    # A factor on the mixer's output that whoever owns it may set (mixers side by side weight their outputs): it rides
+    # in the per-head gated norm, before the output projection, which is linear.
+    takes_output_scale = True
+    output_scale = 1.0
 
     @staticmethod
     def _dims(spec):
@@ -279,7 +283,7 @@ class Retention(Part):
             ops.lightning_recurrence(qkv, cache.state, ctx.cu_q, ctx.slots, ctx.n_seqs, self.decay, h, d, v, o,
                                      max_q_len=ctx.max_q_len, buf=buf, activation=False)
         y = rt.empty(n, h * v)
-        ops.group_gated_norm(o, proj, self.gate_col, None, self.eps, y, v, gate="silu")
+        ops.group_gated_norm(o, proj, self.gate_col, None, self.eps, y, v, gate="silu", scale=self.output_scale)
         return rt.linear(y, self.w_o, out_dtype=f32, residual=residual)
 
 
